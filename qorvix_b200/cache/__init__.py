@@ -1,2 +1,2 @@
 from .manager import CacheManager, LayerCacheView, OutOfPages, OutOfSlots, PageError
-from .spec import FixedStateSpec, PagedKVSpec
+from .spec import FixedStateSpec, PagedKVSpec, PagedRowsSpec

@@ -26,7 +26,7 @@ from typing import Dict, Hashable, List, Optional, Sequence, Tuple
 import torch
 
 from . import native
-from .spec import FixedStateSpec, PagedKVSpec
+from .spec import FixedStateSpec, PagedKVSpec, PagedRowsSpec
 
 
 
@@ -114,7 +114,7 @@ class CacheManager:
         self._paged: List[int] = []
         windows: List[int] = []
         for gi, g in enumerate(self.groups):
-            if isinstance(g.spec, PagedKVSpec):
+            if isinstance(g.spec, (PagedKVSpec, PagedRowsSpec)):
                 self._paged.append(gi)
                 windows.append(int(g.spec.window))
             elif not isinstance(g.spec, FixedStateSpec):
@@ -131,6 +131,11 @@ class CacheManager:
                 if allocate:
                     g.tensor = torch.zeros((len(g.layers), self.num_pages + 1, 2, g.spec.num_kv_heads,
                                             self.page_size, g.spec.head_dim), device=self.device, dtype=dtype)
+            elif isinstance(g.spec, PagedRowsSpec):
+                g.pool = _PoolView(self, self._native_index[gi])
+                if allocate:
+                    g.tensor = torch.zeros((len(g.layers), self.num_pages + 1, self.page_size, g.spec.width),
+                                           device=self.device, dtype=dtype)
             elif allocate:
                 # one more slot than requests: the last is scratch for padded rows of a captured step
                 g.tensor = torch.zeros((len(g.layers), self.max_requests + 1, *g.spec.shape),

@@ -19,6 +19,17 @@ class PagedKVSpec:
 
 
 @dataclass(frozen=True)
+class PagedRowsSpec:
+    """One row of `width` entries per token, in pages (a compressed latent that keys and values
+    are both made from, for instance).  window as for PagedKVSpec."""
+    width: int
+    window: int = 0
+
+    def elems_per_token(self) -> int:
+        return self.width
+
+
+@dataclass(frozen=True)
 class FixedStateSpec:
     """A state of fixed size per request (a recurrent state, a convolution tail, ...):
     one slot per live request, zeroed when the request is admitted."""

@@ -48,6 +48,8 @@ def lookup_architecture(name: str) -> ArchitectureEntry:
 def architecture_of(raw: dict) -> str:
     archs = raw.get("architectures")
     if not archs:
+        if raw.get("architecture"):                 # some model families write the one name as a string
+            return str(raw["architecture"])
         raise ConfigError("config.json: required key 'architectures' is missing")
     return str(archs[0])
 

@@ -311,6 +311,140 @@ extern "C" int qv_cast_rows(void* out, long long ld_out, const void* in, long lo
   return qv_launch_status();
 }
 
+// ---------------------------------------------------------------- embedding + hashed pair table
+// out[t, :] = table[ids[t], :] + pair[row, :] as float32, where row hashes the token with the one before
+// it in its request: (prev * mul_prev + id * mul_cur) mod buckets, and is `buckets` (the table's last row)
+// for a request's first token.  The token before a segment's first one is kept per request in
+// last_token[slot] (int32), which the block of a segment's first token reads and then sets to the
+// segment's last token, so that portions cut anywhere see the same pairs.
+template <typename TW>
+__global__ void embed_pair_kernel(float* __restrict__ out, const TW* __restrict__ table, const TW* __restrict__ pair,
+                                  const int* __restrict__ ids, const int* __restrict__ tok_pos, const int* __restrict__ tok_seg,
+                                  const int* __restrict__ seg_q_start, const int* __restrict__ seg_slot,
+                                  int* __restrict__ last_token, int d, int vocab, int buckets, int mul_prev, int mul_cur) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const int t = blockIdx.x;
+  int id = ids[t];
+  if (id < 0 || id >= vocab) id = 0;
+  const int s = tok_seg[t];
+  const int first = seg_q_start[s];
+  long long row = buckets;
+  if (tok_pos[t] > 0) {
+    int prev = t > first ? ids[t - 1] : last_token[seg_slot[s]];
+    if (prev < 0 || prev >= vocab) prev = 0;
+    row = ((long long)prev * mul_prev + (long long)id * mul_cur) % buckets;
+  }
+  __syncthreads();                          // every thread has read the kept token before it is replaced
+  if (t == first && threadIdx.x == 0) last_token[seg_slot[s]] = ids[seg_q_start[s + 1] - 1];
+  const TW* a = table + (size_t)id * d;
+  const TW* b = pair + (size_t)row * d;
+  float* o = out + (size_t)t * d;
+  for (int i = threadIdx.x; i < d; i += blockDim.x) o[i] = to_f(a[i]) + to_f(b[i]);
+}
+
+extern "C" int qv_embed_pair(float* out, const void* table, const void* pair, const int* ids, const int* tok_pos,
+                             const int* tok_seg, const int* seg_q_start, const int* seg_slot, int* last_token, int T, int d,
+                             int vocab, int buckets, int mul_prev, int mul_cur, int table_dt, void* stream) {
+  if (T <= 0) return 0;
+  if (buckets <= 0) return QV_ERR_UNSUPPORTED;
+  QV_DISPATCH_DT(table_dt, TW,
+                 return qv_launch(embed_pair_kernel<TW>, dim3(T), dim3(256), 0, (cudaStream_t)stream, out, (const TW*)table,
+                                  (const TW*)pair, ids, tok_pos, tok_seg, seg_q_start, seg_slot, last_token, d, vocab, buckets,
+                                  mul_prev, mul_cur));
+  return QV_ERR_UNSUPPORTED;
+}
+
+// ---------------------------------------------------------------- add + two rmsnorms of the same stream
+// x = residual[r] (+ delta[r]), written back; out1[r] = x * rsqrt(mean(x^2) + eps) * w1, out2[r] likewise
+// with w2: the two norms of a block whose mixer and feed-forward both read the stream as it enters.
+template <typename TD, typename TO>
+__global__ void __launch_bounds__(256) add_rmsnorm2_kernel(TO* __restrict__ out1, TO* __restrict__ out2, float* __restrict__ residual,
+                                                           const TD* __restrict__ delta, const float* __restrict__ w1,
+                                                           const float* __restrict__ w2, int d, float eps) {
+  extern __shared__ float smem[];
+  pdl_wait();
+  pdl_launch_dependents();
+  float* xs = smem;
+  float* red = smem + d;
+  const int r = blockIdx.x;
+  float* res = residual + (size_t)r * d;
+  const TD* dl = delta ? delta + (size_t)r * d : nullptr;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < d; i += blockDim.x) {
+    float x = res[i];
+    if (dl) { x += to_f(dl[i]); res[i] = x; }
+    xs[i] = x;
+    ss += x * x;
+  }
+  const float total = block_sum(ss, red);
+  const float scale = 1.0f / sqrtf(total / (float)d + eps);
+  for (int i = threadIdx.x; i < d; i += blockDim.x) {
+    const float v = xs[i] * scale;
+    out1[(size_t)r * d + i] = from_f<TO>(v * w1[i]);
+    if (out2) out2[(size_t)r * d + i] = from_f<TO>(v * w2[i]);
+  }
+}
+
+extern "C" int qv_add_rmsnorm2(void* out1, void* out2, float* residual, const void* delta, const float* w1, const float* w2,
+                               int rows, int d, float eps, int delta_dt, int out_dt, void* stream) {
+  if (rows <= 0) return 0;
+  const size_t smem = (size_t)(d + 33) * sizeof(float);
+  if (smem > 200 * 1024) return QV_ERR_TOO_LARGE;
+  cudaStream_t st = (cudaStream_t)stream;
+#define LAUNCH_NORM2(TD, TO)                                                                                     \
+  do {                                                                                                           \
+    if (smem > 48 * 1024) cudaFuncSetAttribute(add_rmsnorm2_kernel<TD, TO>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+    return qv_launch(add_rmsnorm2_kernel<TD, TO>, dim3(rows), dim3(256), smem, st, (TO*)out1, (TO*)out2, residual, \
+                     (const TD*)delta, w1, w2, d, eps);                                                          \
+  } while (0)
+  if (delta_dt == QV_DT_F32 && out_dt == QV_DT_F32) LAUNCH_NORM2(float, float);
+  else if (delta_dt == QV_DT_BF16 && out_dt == QV_DT_BF16) LAUNCH_NORM2(bf16, bf16);
+  else if (delta_dt == QV_DT_F32 && out_dt == QV_DT_BF16) LAUNCH_NORM2(float, bf16);
+  else if (delta_dt == QV_DT_BF16 && out_dt == QV_DT_F32) LAUNCH_NORM2(bf16, float);
+#undef LAUNCH_NORM2
+  return QV_ERR_UNSUPPORTED;
+}
+
+// ---------------------------------------------------------------- sum of two deltas, tanh cap
+// out (float32) = a + b, each float32 or the compute type: what a block that runs two parts side by side
+// hands on as one delta.
+template <typename TA, typename TB>
+__global__ void sum2_kernel(float* __restrict__ out, const TA* __restrict__ a, const TB* __restrict__ b, size_t n) {
+  pdl_wait();
+  pdl_launch_dependents();
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
+    out[i] = to_f(a[i]) + to_f(b[i]);
+}
+
+extern "C" int qv_sum2(float* out, const void* a, const void* b, long long n, int a_dt, int b_dt, void* stream) {
+  if (n <= 0) return 0;
+  const int blocks = (int)((n + 255) / 256 < 148 * 16 ? (n + 255) / 256 : 148 * 16);
+  cudaStream_t st = (cudaStream_t)stream;
+#define QV_SUM2(TA, TB) return qv_launch(sum2_kernel<TA, TB>, dim3(blocks), dim3(256), 0, st, out, (const TA*)a, (const TB*)b, (size_t)n)
+  if (a_dt == QV_DT_F32 && b_dt == QV_DT_F32) QV_SUM2(float, float);
+  if (a_dt == QV_DT_BF16 && b_dt == QV_DT_BF16) QV_SUM2(bf16, bf16);
+  if (a_dt == QV_DT_F32 && b_dt == QV_DT_BF16) QV_SUM2(float, bf16);
+  if (a_dt == QV_DT_BF16 && b_dt == QV_DT_F32) QV_SUM2(bf16, float);
+#undef QV_SUM2
+  return QV_ERR_UNSUPPORTED;
+}
+
+// x = cap * tanh(x / cap) in place, float32 (a soft limit on logits).
+__global__ void softcap_kernel(float* __restrict__ x, size_t n, float cap) {
+  pdl_wait();
+  pdl_launch_dependents();
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
+    x[i] = cap * tanhf(x[i] / cap);
+}
+
+extern "C" int qv_softcap(float* x, long long n, float cap, void* stream) {
+  if (n <= 0) return 0;
+  if (!(cap > 0.f)) return QV_ERR_UNSUPPORTED;
+  const int blocks = (int)((n + 255) / 256 < 148 * 16 ? (n + 255) / 256 : 148 * 16);
+  return qv_launch(softcap_kernel, dim3(blocks), dim3(256), 0, (cudaStream_t)stream, x, (size_t)n, cap);
+}
+
 extern "C" const char* qv_error_string(int code) {
   if (code == QV_ERR_UNSUPPORTED) return "size or dtype not supported by this kernel";
   if (code == QV_ERR_TOO_LARGE) return "size exceeds what this kernel can hold on chip";

@@ -1,0 +1,254 @@
+// Routed feed-forward (mixture of experts): router, grouping of tokens by expert, the experts' products
+// over the grouped rows, and the weighted sum back into token order.
+//
+// qv_moe_route    logits = Wr h in float32 (fixed summation order), the `top` largest per token (ties: the lower
+//                 index), weights = softmax over the chosen logits only; optionally one more row of the router
+//                 matrix' companion (a scalar gate per token: sigmoid(ws . h)).
+// qv_moe_group    counting sort of the (token, choice) pairs by expert, all on the device (a step never waits
+//                 for the host): row_token[r] = token of sorted row r, slot_row[token * top + j] = its sorted row,
+//                 and a table of row tiles (expert, first row, rows) for the products' grids.
+// qv_moe_experts  CUDA-core products over the grouped rows, float32 multiply-adds with k ascending:
+//                   UP:   act[r] = silu(Wg_e h[row_token[r]]) * (Wu_e h[row_token[r]])
+//                   DOWN: y[r]   = Wd_e act[r]   (float32)
+// qv_moe_combine  delta[t] = (mixer output) + sum_j weight[t, j] * y[slot_row[t, j]] + gate[t] * shared[t]
+//                 in float32, choices summed in the order the router ranked them.
+#include "common.cuh"
+
+template <typename T, typename TW>
+__global__ void __launch_bounds__(128) moe_route_kernel(int* __restrict__ top_idx, float* __restrict__ top_w, float* __restrict__ gate_out,
+                                                        const T* __restrict__ h, int ld_h, const TW* __restrict__ wr,
+                                                        const TW* __restrict__ wg, int d, int E, int top) {
+  extern __shared__ float logit[];           // E floats
+  pdl_wait();
+  pdl_launch_dependents();
+  const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const T* x = h + (size_t)t * ld_h;
+  for (int e = warp; e < E + (wg ? 1 : 0); e += 4) {
+    const TW* w = e < E ? wr + (size_t)e * d : wg;
+    float acc = 0.f;
+    for (int i = lane; i < d; i += 32) acc = fmaf(to_f(w[i]), to_f(x[i]), acc);
+    acc = warp_sum(acc);
+    if (lane == 0) {
+      if (e < E) logit[e] = acc;
+      else gate_out[t] = 1.0f / (1.0f + expf(-acc));
+    }
+  }
+  __syncthreads();
+  if (warp != 0) return;
+  float first = 0.f, denom = 0.f;
+  for (int j = 0; j < top; ++j) {
+    float best = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int e = lane; e < E; e += 32) {
+      const float v = logit[e];
+      if (v > best) { best = v; bi = e; }      // ascending e: the lowest index wins a tie within a lane
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+    }
+    if (j == 0) first = best;
+    const float p = expf(best - first);         // the first choice is the largest: exponents are <= 0
+    denom += p;
+    if (lane == 0) {
+      top_idx[(size_t)t * top + j] = bi;
+      top_w[(size_t)t * top + j] = p;
+      logit[bi] = -INFINITY;
+    }
+    __syncwarp();
+  }
+  for (int j = lane; j < top; j += 32) top_w[(size_t)t * top + j] /= denom;
+}
+
+extern "C" int qv_moe_route(int* top_idx, float* top_w, float* gate_out, const void* h, int ld_h, const void* wr, const void* wg,
+                            int T, int d, int E, int top, int dt, int w_dt, void* stream) {
+  if (T <= 0) return 0;
+  if (E <= 0 || top <= 0 || top > E || E > 8192) return QV_ERR_UNSUPPORTED;
+  cudaStream_t st = (cudaStream_t)stream;
+  const size_t smem = (size_t)E * sizeof(float);
+#define ROUTE(TT, TW) return qv_launch(moe_route_kernel<TT, TW>, dim3(T), dim3(128), smem, st, top_idx, top_w, gate_out, (const TT*)h, ld_h, (const TW*)wr, (const TW*)wg, d, E, top)
+  if (dt == QV_DT_F32 && w_dt == QV_DT_F32) ROUTE(float, float);
+  if (dt == QV_DT_BF16 && w_dt == QV_DT_BF16) ROUTE(bf16, bf16);
+  if (dt == QV_DT_BF16 && w_dt == QV_DT_F32) ROUTE(bf16, float);
+  if (dt == QV_DT_F32 && w_dt == QV_DT_BF16) ROUTE(float, bf16);
+#undef ROUTE
+  return QV_ERR_UNSUPPORTED;
+}
+
+// One block.  tiles: [max_tiles][3] = (expert or -1, first sorted row, rows).
+__global__ void __launch_bounds__(1024) moe_group_kernel(int* __restrict__ row_token, int* __restrict__ slot_row, int* __restrict__ tiles,
+                                                         int max_tiles, const int* __restrict__ top_idx, int* __restrict__ rank_tmp,
+                                                         int R, int top, int E, int bm) {
+  extern __shared__ int cnt[];               // E counts, then E offsets
+  pdl_wait();
+  pdl_launch_dependents();
+  int* off = cnt + E;
+  for (int e = threadIdx.x; e < E; e += blockDim.x) cnt[e] = 0;
+  __syncthreads();
+  for (int r = threadIdx.x; r < R; r += blockDim.x) rank_tmp[r] = atomicAdd(&cnt[top_idx[r]], 1);
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int o = 0, n = 0;
+    for (int e = 0; e < E; ++e) {
+      off[e] = o;
+      for (int r0 = 0; r0 < cnt[e] && n < max_tiles; r0 += bm, ++n) {
+        tiles[3 * n] = e;
+        tiles[3 * n + 1] = o + r0;
+        tiles[3 * n + 2] = cnt[e] - r0 < bm ? cnt[e] - r0 : bm;
+      }
+      o += cnt[e];
+    }
+    for (; n < max_tiles; ++n) { tiles[3 * n] = -1; tiles[3 * n + 1] = 0; tiles[3 * n + 2] = 0; }
+  }
+  __syncthreads();
+  for (int r = threadIdx.x; r < R; r += blockDim.x) {
+    const int pos = off[top_idx[r]] + rank_tmp[r];
+    slot_row[r] = pos;
+    row_token[pos] = r / top;
+  }
+}
+
+#define MOE_BM 32
+#define MOE_BN 64
+#define MOE_BK 16
+
+extern "C" int qv_moe_max_tiles(int R, int E) {
+  const int a = (R + MOE_BM - 1) / MOE_BM + E;
+  return a < R ? a : R;
+}
+
+extern "C" int qv_moe_group(int* row_token, int* slot_row, int* tiles, const int* top_idx, int* rank_tmp, int T, int top, int E,
+                            void* stream) {
+  if (T <= 0) return 0;
+  if (E > 8192) return QV_ERR_UNSUPPORTED;
+  const int R = T * top;
+  return qv_launch(moe_group_kernel, dim3(1), dim3(1024), (size_t)2 * E * sizeof(int), (cudaStream_t)stream, row_token, slot_row, tiles,
+                   qv_moe_max_tiles(R, E), top_idx, rank_tmp, R, top, E, MOE_BM);
+}
+
+// Tile of 32 rows x 64 columns, 256 threads, each 2 rows x 4 columns; k in steps of 16, ascending.
+// UP: a = h (rows gathered by row_token), w1/w2 = gate/up matrices [E][N][K]; out act [R, N] in the compute type.
+// DOWN: a = act [R, K]; w1 = down matrices [E][N][K]; out y [R, N] float32.
+template <typename T, typename TW, bool UP>
+__global__ void __launch_bounds__(256) moe_experts_kernel(void* __restrict__ out_, int ld_out, const T* __restrict__ a, int ld_a,
+                                                          const TW* __restrict__ w1, const TW* __restrict__ w2,
+                                                          const int* __restrict__ row_token, const int* __restrict__ tiles, int N, int K) {
+  __shared__ float As[MOE_BK][MOE_BM + 1];
+  __shared__ float B1[MOE_BK][MOE_BN + 1];
+  __shared__ float B2[UP ? MOE_BK : 1][MOE_BN + 1];
+  pdl_wait();
+  pdl_launch_dependents();
+  const int e = tiles[3 * blockIdx.y];
+  if (e < 0) return;
+  const int row0 = tiles[3 * blockIdx.y + 1], rows = tiles[3 * blockIdx.y + 2];
+  const int n0 = blockIdx.x * MOE_BN;
+  const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+  const TW* W1 = w1 + (size_t)e * N * K;
+  const TW* W2 = UP ? w2 + (size_t)e * N * K : nullptr;
+  float acc1[2][4] = {}, acc2[2][4] = {};
+  // loaders: A tile 32 x 16 (2 elements a thread), B tiles 64 x 16 (4 elements a thread)
+  const int ar = threadIdx.x >> 3, ak = (threadIdx.x & 7) * 2;
+  size_t a_row = 0;
+  const bool a_ok = ar < rows;
+  if (a_ok) a_row = UP ? (size_t)row_token[row0 + ar] : (size_t)(row0 + ar);
+  const int bn = threadIdx.x >> 2, bk = (threadIdx.x & 3) * 4;
+  for (int k0 = 0; k0 < K; k0 += MOE_BK) {
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const int k = k0 + ak + i;
+      As[ak + i][ar] = (a_ok && k < K) ? to_f(a[a_row * ld_a + k]) : 0.f;
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int k = k0 + bk + i, n = n0 + bn;
+      const bool ok = n < N && k < K;
+      B1[bk + i][bn] = ok ? to_f(W1[(size_t)n * K + k]) : 0.f;
+      if (UP) B2[bk + i][bn] = ok ? to_f(W2[(size_t)n * K + k]) : 0.f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < MOE_BK; ++k) {
+      const float a0 = As[k][ty * 2], a1 = As[k][ty * 2 + 1];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        const float b = B1[k][tx * 4 + c];
+        acc1[0][c] = fmaf(a0, b, acc1[0][c]);
+        acc1[1][c] = fmaf(a1, b, acc1[1][c]);
+        if (UP) {
+          const float b2 = B2[k][tx * 4 + c];
+          acc2[0][c] = fmaf(a0, b2, acc2[0][c]);
+          acc2[1][c] = fmaf(a1, b2, acc2[1][c]);
+        }
+      }
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    const int row = ty * 2 + r;
+    if (row >= rows) continue;
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      const int n = n0 + tx * 4 + c;
+      if (n >= N) continue;
+      if (UP) {
+        const float g = acc1[r][c];
+        ((T*)out_)[(size_t)(row0 + row) * ld_out + n] = from_f<T>(g / (1.0f + expf(-g)) * acc2[r][c]);
+      } else {
+        ((float*)out_)[(size_t)(row0 + row) * ld_out + n] = acc1[r][c];
+      }
+    }
+  }
+}
+
+extern "C" int qv_moe_experts(int up, void* out, int ld_out, const void* a, int ld_a, const void* w1, const void* w2,
+                              const int* row_token, const int* tiles, int R, int E, int N, int K, int dt, int w_dt, void* stream) {
+  if (R <= 0) return 0;
+  const int max_tiles = qv_moe_max_tiles(R, E);
+  if (max_tiles > 65535) return QV_ERR_TOO_LARGE;
+  dim3 grid((N + MOE_BN - 1) / MOE_BN, max_tiles);
+  cudaStream_t st = (cudaStream_t)stream;
+#define EXPERTS(TT, TW)                                                                                                        \
+  do {                                                                                                                         \
+    if (up) return qv_launch(moe_experts_kernel<TT, TW, true>, grid, dim3(256), 0, st, out, ld_out, (const TT*)a, ld_a, (const TW*)w1, \
+                             (const TW*)w2, row_token, tiles, N, K);                                                           \
+    return qv_launch(moe_experts_kernel<TT, TW, false>, grid, dim3(256), 0, st, out, ld_out, (const TT*)a, ld_a, (const TW*)w1,  \
+                     (const TW*)w2, row_token, tiles, N, K);                                                                   \
+  } while (0)
+  if (dt == QV_DT_F32 && w_dt == QV_DT_F32) EXPERTS(float, float);
+  if (dt == QV_DT_BF16 && w_dt == QV_DT_BF16) EXPERTS(bf16, bf16);
+  if (dt == QV_DT_BF16 && w_dt == QV_DT_F32) EXPERTS(bf16, float);
+  if (dt == QV_DT_F32 && w_dt == QV_DT_BF16) EXPERTS(float, bf16);
+#undef EXPERTS
+  return QV_ERR_UNSUPPORTED;
+}
+
+// delta [T, d] float32.  mix, shared: [T, d] in the compute type or null; gate [T] float32 or null.
+template <typename T>
+__global__ void __launch_bounds__(256) moe_combine_kernel(float* __restrict__ delta, const T* __restrict__ mix, const float* __restrict__ y,
+                                                          const int* __restrict__ slot_row, const float* __restrict__ top_w,
+                                                          const T* __restrict__ shared, const float* __restrict__ gate, int d, int top) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const int t = blockIdx.x;
+  const float g = gate ? gate[t] : 1.f;
+  for (int i = threadIdx.x; i < d; i += blockDim.x) {
+    float routed = 0.f;
+    for (int j = 0; j < top; ++j) routed = fmaf(top_w[(size_t)t * top + j], y[(size_t)slot_row[(size_t)t * top + j] * d + i], routed);
+    float v = routed;
+    if (shared) v = fmaf(g, to_f(shared[(size_t)t * d + i]), v);
+    if (mix) v += to_f(mix[(size_t)t * d + i]);
+    delta[(size_t)t * d + i] = v;
+  }
+}
+
+extern "C" int qv_moe_combine(float* delta, const void* mix, const float* y, const int* slot_row, const float* top_w,
+                              const void* shared, const float* gate, int T, int d, int top, int dt, void* stream) {
+  if (T <= 0) return 0;
+  QV_DISPATCH_DT(dt, TT,
+                 return qv_launch(moe_combine_kernel<TT>, dim3(T), dim3(256), 0, (cudaStream_t)stream, delta, (const TT*)mix, y, slot_row,
+                                  top_w, (const TT*)shared, gate, d, top));
+  return QV_ERR_UNSUPPORTED;
+}

@@ -54,10 +54,26 @@ _ARGTYPES = {
     "qv_attn_set_decode_variant": [_I],
     "qv_attn_set_error_word": [_V],
     "qv_attn_decode_bf16": [_V, _I, _V, _I, _V, _V, _V, _V, _I, _I, _I, _I, _I, _I, _I, _F, _I, _V, _V],
+    "qv_embed_pair": [_V, _V, _V, _V, _V, _V, _V, _V, _V, _I, _I, _I, _I, _I, _I, _I, _V],
+    "qv_add_rmsnorm2": [_V, _V, _V, _V, _V, _V, _I, _I, _F, _I, _I, _V],
+    "qv_sum2": [_V, _V, _V, _L, _I, _I, _V],
+    "qv_softcap": [_V, _L, _F, _V],
+    "qv_latent_prepare": [_V, _I, _I, _I, _V, _V, _F, _V, _I, _V, _V, _V, _I, _I, _I, _I, _I, _I, _I, _I, _I, _V],
+    "qv_latent_attention_generic": [_V, _I, _V, _I, _V, _I, _V, _V, _V, _V, _V, _V, _I, _I, _I, _I, _I, _I, _I, _I, _I, _F, _I, _I, _V],
+    "qv_conv_state": [_V, _I, _V, _I, _V, _V, _V, _L, _V, _V, _I, _I, _I, _I, _I, _V],
+    "qv_linear_scan_state_floats": [_I, _I, _I, _I],
+    "qv_linear_scan": [_I, _V, _I, _V, _I, _I, _V, _I, _V, _I, _V, _I, _V, _I, _V, _V, _V, _F, _F, _V, _L, _V, _V, _I, _I, _I, _I, _I, _V],
+    "qv_gated_group_norm": [_V, _I, _V, _I, _V, _I, _V, _I, _I, _I, _F, _I, _I, _V],
+    "qv_moe_route": [_V, _V, _V, _V, _I, _V, _V, _I, _I, _I, _I, _I, _I, _V],
+    "qv_moe_max_tiles": [_I, _I],
+    "qv_moe_group": [_V, _V, _V, _V, _V, _I, _I, _I, _V],
+    "qv_moe_experts": [_I, _V, _I, _V, _I, _V, _V, _V, _V, _I, _I, _I, _I, _I, _I, _V],
+    "qv_moe_combine": [_V, _V, _V, _V, _V, _V, _V, _I, _I, _I, _I, _V],
     "qv_argmax": [_V, _V, _I, _I, _L, _V],
     "qv_sample": [_V, _V, _I, _I, _L, _V, _V, _V, _V, _V, _V, _I, _V, _V, _V, _V],
 }
-_RESTYPES = {"qv_error_string": ctypes.c_char_p, "qv_packed_weight_bytes": c_longlong, "qv_gemm_bf16_split_slot_bytes": c_longlong}
+_RESTYPES = {"qv_error_string": ctypes.c_char_p, "qv_packed_weight_bytes": c_longlong, "qv_gemm_bf16_split_slot_bytes": c_longlong,
+             "qv_linear_scan_state_floats": c_longlong}
 _typed_libs = {}
 
 
@@ -207,6 +223,201 @@ def cast_rows(out, src) -> None:
     rc = _lib("elementwise").qv_cast_rows(_ptr(out), out.stride(0), _ptr(src), src.stride(0), src.shape[0], src.shape[1],
                                           dt_code(src.dtype), dt_code(out.dtype), _stream())
     _check(rc, "cast_rows")
+
+
+def embed_pair(out, table, pair, ids, ctx, last_token, buckets: int, mul_prev: int, mul_cur: int) -> None:
+    """out[t] (float32) = table[ids[t]] + pair[hash of (token before, token)]; the request's first token takes
+    pair's last row.  last_token [slots] int32 keeps each request's latest token between steps."""
+    _need_cuda(out, table, pair, ids, last_token)
+    _i32(ids, "ids"); _i32(last_token, "last_token")
+    T, d = out.shape
+    assert out.dtype == torch.float32 and out.is_contiguous() and table.is_contiguous() and pair.is_contiguous()
+    assert table.shape[1] == d and pair.shape == (buckets + 1, d) and pair.dtype == table.dtype
+    rc = _lib("elementwise").qv_embed_pair(
+        _ptr(out), _ptr(table), _ptr(pair), _ptr(ids), _ptr(ctx.tok_pos), _ptr(ctx.tok_seg), _ptr(ctx.seg_q_start),
+        _ptr(ctx.seg_slot), _ptr(last_token), T, d, table.shape[0], buckets, mul_prev, mul_cur, dt_code(table.dtype), _stream())
+    _check(rc, "embed_pair")
+
+
+def add_rmsnorm2(out1, out2, residual, delta, w1, w2, eps: float) -> None:
+    """residual (float32) += delta; out1 = rmsnorm(residual) * w1 and out2 = rmsnorm(residual) * w2 (out2 and
+    w2 may be None): the two norms of a block whose parts read the same stream, in one pass."""
+    _need_cuda(out1, out2, residual, delta, w1, w2)
+    rows, d = out1.shape
+    assert residual.dtype == torch.float32 and residual.is_contiguous() and residual.shape == (rows, d)
+    assert out1.is_contiguous() and w1.dtype == torch.float32 and w1.numel() == d
+    if out2 is not None:
+        assert out2.is_contiguous() and out2.shape == out1.shape and out2.dtype == out1.dtype and w2.dtype == torch.float32
+    if delta is not None:
+        assert delta.is_contiguous() and delta.shape == residual.shape
+    ddt = dt_code(delta.dtype) if delta is not None else dt_code(out1.dtype)
+    rc = _lib("elementwise").qv_add_rmsnorm2(_ptr(out1), _ptr(out2), _ptr(residual), _ptr(delta), _ptr(w1), _ptr(w2), rows, d,
+                                             eps, ddt, dt_code(out1.dtype), _stream())
+    _check(rc, "add_rmsnorm2")
+
+
+def sum2(out, a, b) -> None:
+    """out (float32) = a + b, elementwise."""
+    _need_cuda(out, a, b)
+    assert out.dtype == torch.float32 and out.is_contiguous() and a.is_contiguous() and b.is_contiguous()
+    assert a.numel() == out.numel() == b.numel()
+    _check(_lib("elementwise").qv_sum2(_ptr(out), _ptr(a), _ptr(b), out.numel(), dt_code(a.dtype), dt_code(b.dtype), _stream()), "sum2")
+
+
+def softcap(x, cap: float) -> None:
+    """x = cap * tanh(x / cap) in place (float32)."""
+    _need_cuda(x)
+    assert x.dtype == torch.float32 and x.is_contiguous()
+    _check(_lib("elementwise").qv_softcap(_ptr(x), x.numel(), float(cap), _stream()), "softcap")
+
+
+# ------------------------------------------------------------------ latent attention
+
+def latent_prepare(proj, q_off: int, kv_off: int, cache_layer, norm_w, eps, cos_sin, ctx, block_table, H, dn, dr, rank, rot, page) -> None:
+    """Per token of proj (rows [.. q: H*(dn+dr) at q_off .. down: rank+dr at kv_off ..]): the latent part of the
+    down projection RMS-normed, the shared key part rotated (pairs 2i, 2i+1), both written to the token's row of
+    cache_layer [pages, page, rank+dr]; every head's rotated query part rotated in place."""
+    _need_cuda(proj, cache_layer, norm_w, cos_sin, block_table)
+    assert proj.stride(1) == 1 and cache_layer.is_contiguous() and cache_layer.dtype == proj.dtype
+    assert tuple(cache_layer.shape[1:]) == (page, rank + dr) and norm_w.dtype == torch.float32 and norm_w.numel() == rank
+    assert cos_sin.dtype == torch.float32 and cos_sin.is_contiguous() and cos_sin.shape[1] * 2 == rot
+    _i32(block_table, "block_table")
+    rc = _lib("latent_attention").qv_latent_prepare(
+        _ptr(proj), proj.stride(0), q_off, kv_off, _ptr(cache_layer), _ptr(norm_w), eps, _ptr(cos_sin), cos_sin.shape[0],
+        _ptr(ctx.tok_pos), _ptr(ctx.tok_seg), _ptr(block_table), block_table.shape[-1], proj.shape[0], H, dn, dr, rank, rot, page,
+        dt_code(proj.dtype), _stream())
+    _check(rc, "latent_prepare")
+
+
+def latent_attention_generic(out, q, gate, cache_layer, wuk, wuv, ctx, block_table, H, dn, dr, dv, rank, page, window, scale) -> None:
+    """out[t, h*dv:(h+1)*dv] = gate * Wuv_h (softmax-weighted latent) for every token and head, the query carried
+    into the latent space by Wuk_h; float32 arithmetic, any sizes.  q: [T, H*(dn+dr)] (a column slice is fine)."""
+    _need_cuda(out, q, gate, cache_layer, wuk, wuv, block_table)
+    assert q.stride(1) == 1 and out.stride(1) == 1 and q.dtype == out.dtype == cache_layer.dtype
+    assert cache_layer.is_contiguous() and tuple(cache_layer.shape[1:]) == (page, rank + dr)
+    assert wuk.is_contiguous() and tuple(wuk.shape) == (H * dn, rank) and wuv.is_contiguous() and tuple(wuv.shape) == (H * dv, rank)
+    assert wuk.dtype == wuv.dtype
+    if gate is not None:
+        assert gate.stride(1) == 1 and gate.dtype == out.dtype
+    _i32(block_table, "block_table")
+    rc = _lib("latent_attention").qv_latent_attention_generic(
+        _ptr(out), out.stride(0), _ptr(q), q.stride(0), _ptr(gate), gate.stride(0) if gate is not None else 0, _ptr(cache_layer),
+        _ptr(wuk), _ptr(wuv), _ptr(ctx.tok_pos), _ptr(ctx.tok_seg), _ptr(block_table), block_table.shape[-1], q.shape[0], H, dn, dr,
+        dv, rank, page, window, scale, dt_code(q.dtype), dt_code(wuk.dtype), _stream())
+    _check(rc, "latent_attention_generic")
+
+
+def latent_attention(out, q, gate, cache_layer, wuk, wuv, ctx, block_table, H, dn, dr, dv, rank, page, window, scale) -> None:
+    """Latent attention of every token of the step with the kernel that fits the dtype and the sizes."""
+    latent_attention_generic(out, q, gate, cache_layer, wuk, wuv, ctx, block_table, H, dn, dr, dv, rank, page, window, scale)
+
+
+# ------------------------------------------------------------------ recurrent mixers
+
+SCAN_GATED_MAX, SCAN_DECAY = 0, 1
+
+
+def conv_state(out, x, w, bias, tail, ctx) -> None:
+    """out = silu(causal convolution of x along each request's tokens + bias), per channel; w [channels, taps]
+    float32 with the current token's tap last; tail [slots, (taps-1)*channels] float32 keeps each request's
+    last inputs and is brought up to date."""
+    _need_cuda(out, x, w, bias, tail)
+    T, C = x.shape
+    assert out.shape == x.shape and out.dtype == x.dtype and out.stride(1) == 1 and x.stride(1) == 1
+    assert w.dtype == torch.float32 and w.is_contiguous() and w.shape[0] == C and tail.dtype == torch.float32
+    taps = w.shape[1]
+    assert tail.stride(-1) == 1 and tail.shape[-1] >= (taps - 1) * C
+    rc = _lib("recurrent").qv_conv_state(
+        _ptr(out), out.stride(0), _ptr(x), x.stride(0), _ptr(w), _ptr(bias), _ptr(tail), tail.stride(0), _ptr(ctx.seg_q_start),
+        _ptr(ctx.seg_slot), ctx.num_segments, ctx.max_q_len, C, taps, dt_code(x.dtype), _stream())
+    _check(rc, "conv_state")
+
+
+def linear_scan_state_floats(kind: int, H: int, dk: int, dv: int) -> int:
+    """How many float32 values linear_scan keeps per request for H heads of dk x dv."""
+    return int(_lib("recurrent").qv_linear_scan_state_floats(kind, H, dk, dv))
+
+
+def linear_scan(kind, out, q, k, v, g1, g2, p1, p2, p3, cap, q_scale, state, ctx, H, dk, dv, q_group=1) -> None:
+    """Per request and head: S = a S + b k v^T, out = S^T q (see csrc/recurrent.cu for the two kinds of gates);
+    state [slots, n] float32 is read and left up to date.  q, k: [T, (H/q_group)*dk], v: [T, H*dv] (column slices
+    are fine), g1/g2: float32 [T, >=H] pre-activations, p1..p3: float32 [H] or None; out float32 [T, H*dv]."""
+    _need_cuda(out, q, k, v, g1, g2, p1, p2, p3, state)
+    assert out.dtype == torch.float32 and out.stride(1) == 1 and q.dtype == k.dtype == v.dtype
+    assert q.stride(1) == 1 and k.stride(1) == 1 and v.stride(1) == 1 and g1.dtype == torch.float32 and g1.stride(1) == 1
+    assert state.dtype == torch.float32 and state.stride(-1) == 1
+    for p in (p1, p2, p3):
+        assert p is None or (p.dtype == torch.float32 and p.numel() >= H)
+    rc = _lib("recurrent").qv_linear_scan(
+        kind, _ptr(out), out.stride(0), _ptr(q), q.stride(0), q_group, _ptr(k), k.stride(0), _ptr(v), v.stride(0), _ptr(g1),
+        g1.stride(0), _ptr(g2), g2.stride(0) if g2 is not None else 0, _ptr(p1), _ptr(p2), _ptr(p3), float(cap), float(q_scale),
+        _ptr(state), state.stride(0), _ptr(ctx.seg_q_start), _ptr(ctx.seg_slot), ctx.num_segments, H, dk, dv, dt_code(q.dtype),
+        _stream())
+    _check(rc, "linear_scan")
+
+
+def gated_group_norm(out, y, gate, w, groups: int, eps: float, gate_first: bool) -> None:
+    """out = unit norm of y (float32) in `groups` equal parts of a row, times w, with the gate applied behind the
+    norm as a sigmoid (gate_first False) or ahead of it as a SiLU (True)."""
+    _need_cuda(out, y, gate, w)
+    T, W = y.shape
+    assert y.dtype == torch.float32 and y.stride(1) == 1 and out.stride(1) == 1 and gate.stride(1) == 1
+    assert out.dtype == gate.dtype and w.dtype == torch.float32 and w.numel() == W
+    rc = _lib("recurrent").qv_gated_group_norm(_ptr(out), out.stride(0), _ptr(y), y.stride(0), _ptr(gate), gate.stride(0), _ptr(w),
+                                               T, W, groups, eps, 1 if gate_first else 0, dt_code(out.dtype), _stream())
+    _check(rc, "gated_group_norm")
+
+
+# ------------------------------------------------------------------ routed feed-forward
+
+def moe_route(top_idx, top_w, gate_out, h, w_router, w_gate) -> None:
+    """Per token: router logits in float32, the top choices (top_idx int32 [T, top]) and their weights (softmax
+    over the chosen logits, top_w float32 [T, top]); gate_out [T] = sigmoid(w_gate . h) when w_gate is given."""
+    _need_cuda(top_idx, top_w, gate_out, h, w_router, w_gate)
+    T, d = h.shape
+    E, top = w_router.shape[0], top_idx.shape[1]
+    assert h.stride(1) == 1 and w_router.is_contiguous() and w_router.shape[1] == d and top_idx.is_contiguous() and top_w.is_contiguous()
+    rc = _lib("moe").qv_moe_route(_ptr(top_idx), _ptr(top_w), _ptr(gate_out), _ptr(h), h.stride(0), _ptr(w_router), _ptr(w_gate),
+                                  T, d, E, top, dt_code(h.dtype), dt_code(w_router.dtype), _stream())
+    _check(rc, "moe_route")
+
+
+def moe_max_tiles(rows: int, experts: int) -> int:
+    return int(_lib("moe").qv_moe_max_tiles(rows, experts))
+
+
+def moe_group(row_token, slot_row, tiles, top_idx, scratch, experts: int) -> None:
+    """Sorts the (token, choice) pairs by expert on the device; see csrc/moe.cu."""
+    _need_cuda(row_token, slot_row, tiles, top_idx, scratch)
+    T, top = top_idx.shape
+    rc = _lib("moe").qv_moe_group(_ptr(row_token), _ptr(slot_row), _ptr(tiles), _ptr(top_idx), _ptr(scratch), T, top, experts, _stream())
+    _check(rc, "moe_group")
+
+
+def moe_experts(up: bool, out, a, w1, w2, row_token, tiles) -> None:
+    """The experts' products over the grouped rows.  up: out[r] = silu(w1[e] x) * (w2[e] x) with x = a[row_token[r]];
+    else out[r] (float32) = w1[e] a[r].  w1, w2: [E, N, K]."""
+    _need_cuda(out, a, w1, w2, row_token, tiles)
+    R = row_token.numel()
+    E, N, K = w1.shape
+    assert w1.is_contiguous() and a.stride(1) == 1 and out.stride(1) == 1 and a.shape[1] == K and out.shape == (R, N)
+    assert out.dtype == (a.dtype if up else torch.float32)
+    rc = _lib("moe").qv_moe_experts(1 if up else 0, _ptr(out), out.stride(0), _ptr(a), a.stride(0), _ptr(w1), _ptr(w2),
+                                    _ptr(row_token), _ptr(tiles), R, E, N, K, dt_code(a.dtype), dt_code(w1.dtype), _stream())
+    _check(rc, "moe_experts")
+
+
+def moe_combine(delta, mix, y, slot_row, top_w, shared, gate) -> None:
+    """delta (float32) = mix + sum_j top_w[t, j] * y[slot_row[t, j]] + gate[t] * shared[t]; mix, shared, gate may be None."""
+    _need_cuda(delta, mix, y, slot_row, top_w, shared, gate)
+    T, d = delta.shape
+    assert delta.dtype == torch.float32 and delta.is_contiguous() and y.dtype == torch.float32 and y.is_contiguous()
+    ref = mix if mix is not None else shared
+    for t in (mix, shared):
+        assert t is None or (t.is_contiguous() and t.shape == delta.shape and t.dtype == ref.dtype)
+    rc = _lib("moe").qv_moe_combine(_ptr(delta), _ptr(mix), _ptr(y), _ptr(slot_row), _ptr(top_w), _ptr(shared), _ptr(gate), T, d,
+                                    top_w.shape[1], dt_code(ref.dtype) if ref is not None else F32, _stream())
+    _check(rc, "moe_combine")
 
 
 # ------------------------------------------------------------------ matrix products

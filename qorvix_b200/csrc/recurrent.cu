@@ -1,0 +1,265 @@
+// Recurrent mixers' kernels: a per-request state of fixed size carried from token to token.
+//
+// qv_conv_state     short causal convolution per channel with bias and SiLU, the last taps-1 inputs of a
+//                   request kept as state so that a portion continues where the last one ended.
+// qv_linear_scan    S_t = a_t S_(t-1) + b_t k_t v_t^T;  y_t = S_t^T q_t  per head, S in float32, in two kinds:
+//                     GATED_MAX  exponential gates stabilised by a running maximum (matrix-memory LSTM):
+//                                log i = cap tanh((gi + bi)/cap), log f = logsigmoid(cap tanh((gf + bf)/cap)),
+//                                m_t = max(log f + m_(t-1), log i), a = exp(log f + m_(t-1) - m_t), b = exp(log i - m_t),
+//                                n_t = a n_(t-1) + b k_t,  y_t = S_t^T q_t / (max(|n_t . q_t|, exp(-m_t)) + 1e-6)
+//                     DECAY      selective state space with a scalar decay per head:
+//                                dt = softplus(g + bias), a = exp(-exp(A_log) dt), b = dt, y_t = S_t^T q_t + D v_t
+// qv_gated_group_norm  the unit norm (RMS over equal parts of a row) with weight and gate that follows a scan.
+//
+// All state arithmetic, gates, decays and norms are float32; q, k and v are read in the compute type.
+#include "common.cuh"
+
+#define CONV_MAX_TAPS 16
+#define CONV_CHUNK 64
+
+// in/out: [T, channels] with row strides; w [channels, taps] (last column: the current token), bias [channels];
+// tail [slots][(taps-1) * channels] float32, oldest input first.  grid (segments, channel tiles, time chunks).
+template <typename T>
+__global__ void __launch_bounds__(128) conv_state_kernel(T* __restrict__ out, int ld_out, const T* __restrict__ in, int ld_in,
+                                                         const float* __restrict__ w, const float* __restrict__ bias,
+                                                         float* __restrict__ tail, long long slot_stride,
+                                                         const int* __restrict__ seg_q_start, const int* __restrict__ seg_slot,
+                                                         int channels, int taps) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const int s = blockIdx.x;
+  const int c = blockIdx.y * 128 + threadIdx.x;
+  const int q0 = seg_q_start[s], len = seg_q_start[s + 1] - q0;
+  const int j0 = blockIdx.z * CONV_CHUNK;
+  if (c >= channels || j0 >= len) return;
+  const int j1 = j0 + CONV_CHUNK < len ? j0 + CONV_CHUNK : len;
+  float* tl = tail + (size_t)seg_slot[s] * slot_stride;
+  float wt[CONV_MAX_TAPS], old[CONV_MAX_TAPS];
+#pragma unroll
+  for (int i = 0; i < CONV_MAX_TAPS; ++i) {
+    wt[i] = i < taps ? w[(size_t)c * taps + i] : 0.f;
+    old[i] = (blockIdx.z == 0 && i < taps - 1) ? tl[(size_t)i * channels + c] : 0.f;
+  }
+  const float b = bias ? bias[c] : 0.f;
+  // a chunk is at least as long as the longest filter, so only the first chunk reaches back into the state
+  for (int j = j0; j < j1; ++j) {
+    float acc = b;
+#pragma unroll
+    for (int i = 0; i < CONV_MAX_TAPS; ++i) {
+      if (i < taps) {
+        const int idx = j - (taps - 1) + i;
+        const float v = idx >= 0 ? to_f(in[(size_t)(q0 + idx) * ld_in + c]) : old[taps - 1 + idx];
+        acc = fmaf(wt[i], v, acc);
+      }
+    }
+    out[(size_t)(q0 + j) * ld_out + c] = from_f<T>(acc / (1.0f + expf(-acc)));
+  }
+  if (blockIdx.z == 0) {
+    for (int i = 0; i < taps - 1; ++i) {
+      const int idx = len - (taps - 1) + i;
+      tl[(size_t)i * channels + c] = idx >= 0 ? to_f(in[(size_t)(q0 + idx) * ld_in + c]) : old[taps - 1 + idx];
+    }
+  }
+}
+
+extern "C" int qv_conv_state(void* out, int ld_out, const void* in, int ld_in, const float* w, const float* bias, float* tail,
+                             long long slot_stride, const int* seg_q_start, const int* seg_slot, int S, int max_q_len,
+                             int channels, int taps, int dt, void* stream) {
+  if (S <= 0 || channels <= 0) return 0;
+  if (taps < 1 || taps > CONV_MAX_TAPS) return QV_ERR_UNSUPPORTED;
+  const int chunks = max_q_len > 0 ? (max_q_len + CONV_CHUNK - 1) / CONV_CHUNK : 1;
+  if (chunks > 65535 || (channels + 127) / 128 > 65535) return QV_ERR_TOO_LARGE;
+  dim3 grid(S, (channels + 127) / 128, chunks);
+  QV_DISPATCH_DT(dt, TT,
+                 return qv_launch(conv_state_kernel<TT>, grid, dim3(128), 0, (cudaStream_t)stream, (TT*)out, ld_out, (const TT*)in,
+                                  ld_in, w, bias, tail, slot_stride, seg_q_start, seg_slot, channels, taps));
+  return QV_ERR_UNSUPPORTED;
+}
+
+// ---------------------------------------------------------------- the scan
+#define SCAN_VT 32          // value columns per block (one per lane)
+#define SCAN_WARPS 8        // the key rows are dealt to the warps
+#define SCAN_GATED_MAX 0
+#define SCAN_DECAY 1
+
+struct ScanArgs {
+  float* out; int ld_out;                 // [T, H * dv] float32
+  const void* q; int ld_q; int q_group;   // head h reads columns (h / q_group) * dk ... of q and of k
+  const void* k; int ld_k;
+  const void* v; int ld_v;                // head h reads columns h * dv ...
+  const float* g1; int ld_g1;             // [T, >= H]: input-gate pre-activation | step pre-activation
+  const float* g2; int ld_g2;             // [T, >= H]: forget-gate pre-activation (GATED_MAX)
+  const float* p1; const float* p2; const float* p3;   // per head: bi | dt bias;  bf | A_log;  - | D
+  float cap; float q_scale;
+  float* state; long long slot_stride;    // per slot: [H][tiles][dk * 32 (+ dk + 1 for GATED_MAX)]
+  const int* seg_q_start; const int* seg_slot;
+  int H, dk, dv;
+};
+
+__host__ __device__ inline int scan_tile_floats(int kind, int dk) { return dk * SCAN_VT + (kind == SCAN_GATED_MAX ? dk + 1 : 0); }
+
+template <typename T, int KIND>
+__global__ void __launch_bounds__(SCAN_VT * SCAN_WARPS) linear_scan_kernel(ScanArgs a) {
+  extern __shared__ float sm[];
+  pdl_wait();
+  pdl_launch_dependents();
+  const int s = blockIdx.x, h = blockIdx.y, tile = blockIdx.z;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int dk = a.dk, dv = a.dv;
+  const int tiles = (dv + SCAN_VT - 1) / SCAN_VT;
+  float* S = sm;                           // [dk][32]
+  float* qs = S + (size_t)dk * SCAN_VT;    // [dk]
+  float* ks = qs + dk;                     // [dk]
+  float* ns = ks + dk;                     // [dk] (GATED_MAX)
+  float* red = ns + dk;                    // [SCAN_WARPS][32]
+  float* sc = red + SCAN_WARPS * SCAN_VT;  // [2]: n . q, spare
+  const int q0 = a.seg_q_start[s], len = a.seg_q_start[s + 1] - q0;
+  float* st = a.state + (size_t)a.seg_slot[s] * a.slot_stride + ((size_t)h * tiles + tile) * scan_tile_floats(KIND, dk);
+  for (int i = threadIdx.x; i < dk * SCAN_VT; i += blockDim.x) S[i] = st[i];
+  float m = 0.f;
+  if (KIND == SCAN_GATED_MAX) {
+    for (int i = threadIdx.x; i < dk; i += blockDim.x) ns[i] = st[dk * SCAN_VT + i];
+    m = st[dk * SCAN_VT + dk];
+  }
+  const int col = tile * SCAN_VT + lane;
+  const bool live = col < dv;
+  const T* qb = (const T*)a.q + (size_t)(h / a.q_group) * dk;
+  const T* kb = (const T*)a.k + (size_t)(h / a.q_group) * dk;
+  const T* vb = (const T*)a.v + (size_t)h * dv;
+  const float b1 = a.p1 ? a.p1[h] : 0.f, b2 = a.p2 ? a.p2[h] : 0.f, b3 = a.p3 ? a.p3[h] : 0.f;
+  __syncthreads();
+  for (int j = 0; j < len; ++j) {
+    const size_t t = (size_t)(q0 + j);
+    for (int i = threadIdx.x; i < dk; i += blockDim.x) {
+      qs[i] = to_f(qb[t * a.ld_q + i]) * a.q_scale;
+      ks[i] = to_f(kb[t * a.ld_k + i]);
+    }
+    const float vv = live ? to_f(vb[t * a.ld_v + col]) : 0.f;
+    float keep, take;
+    if (KIND == SCAN_GATED_MAX) {
+      const float li = a.cap * tanhf((a.g1[t * a.ld_g1 + h] + b1) / a.cap);
+      const float zf = a.cap * tanhf((a.g2[t * a.ld_g2 + h] + b2) / a.cap);
+      const float lf = fminf(zf, 0.f) - log1pf(expf(-fabsf(zf)));          // log sigmoid
+      const float m_new = fmaxf(lf + m, li);
+      keep = expf(lf + m - m_new);
+      take = expf(li - m_new);
+      m = m_new;
+    } else {
+      const float z = a.g1[t * a.ld_g1 + h] + b1;
+      const float dt = z > 20.f ? z : log1pf(expf(z));                      // softplus
+      keep = expf(-expf(b2) * dt);
+      take = dt;
+    }
+    __syncthreads();                       // qs, ks are in place; red of the last token has been read
+    if (KIND == SCAN_GATED_MAX && warp == 0) {
+      float dot = 0.f;
+      for (int i = lane; i < dk; i += 32) {
+        const float n = keep * ns[i] + take * ks[i];
+        ns[i] = n;
+        dot = fmaf(n, qs[i], dot);
+      }
+      dot = warp_sum(dot);
+      if (lane == 0) sc[0] = dot;
+    }
+    float acc = 0.f;
+    const float tv = take * vv;
+    for (int i = warp; i < dk; i += SCAN_WARPS) {
+      const float sv = fmaf(keep, S[i * SCAN_VT + lane], tv * ks[i]);
+      S[i * SCAN_VT + lane] = sv;
+      acc = fmaf(sv, qs[i], acc);
+    }
+    red[warp * SCAN_VT + lane] = acc;
+    __syncthreads();
+    if (warp == 0 && live) {
+      float y = 0.f;
+#pragma unroll
+      for (int w = 0; w < SCAN_WARPS; ++w) y += red[w * SCAN_VT + lane];
+      if (KIND == SCAN_GATED_MAX) y = y / (fmaxf(fabsf(sc[0]), expf(-m)) + 1e-6f);
+      else y = fmaf(b3, vv, y);
+      a.out[t * a.ld_out + (size_t)h * dv + col] = y;
+    }
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < dk * SCAN_VT; i += blockDim.x) st[i] = S[i];
+  if (KIND == SCAN_GATED_MAX) {
+    for (int i = threadIdx.x; i < dk; i += blockDim.x) st[dk * SCAN_VT + i] = ns[i];
+    if (threadIdx.x == 0) st[dk * SCAN_VT + dk] = m;
+  }
+}
+
+extern "C" long long qv_linear_scan_state_floats(int kind, int H, int dk, int dv) {
+  return (long long)H * ((dv + SCAN_VT - 1) / SCAN_VT) * scan_tile_floats(kind, dk);
+}
+
+extern "C" int qv_linear_scan(int kind, float* out, int ld_out, const void* q, int ld_q, int q_group, const void* k, int ld_k,
+                              const void* v, int ld_v, const float* g1, int ld_g1, const float* g2, int ld_g2, const float* p1,
+                              const float* p2, const float* p3, float cap, float q_scale, float* state, long long slot_stride,
+                              const int* seg_q_start, const int* seg_slot, int S, int H, int dk, int dv, int dt, void* stream) {
+  if (S <= 0) return 0;
+  if (kind != SCAN_GATED_MAX && kind != SCAN_DECAY) return QV_ERR_UNSUPPORTED;
+  if (H <= 0 || dk <= 0 || dv <= 0 || q_group <= 0 || H > 65535) return QV_ERR_UNSUPPORTED;
+  const int tiles = (dv + SCAN_VT - 1) / SCAN_VT;
+  const size_t smem = ((size_t)dk * SCAN_VT + 3 * (size_t)dk + SCAN_WARPS * SCAN_VT + 2) * sizeof(float);
+  if (smem > 200 * 1024 || tiles > 65535) return QV_ERR_TOO_LARGE;
+  ScanArgs a;
+  a.out = out; a.ld_out = ld_out; a.q = q; a.ld_q = ld_q; a.q_group = q_group; a.k = k; a.ld_k = ld_k; a.v = v; a.ld_v = ld_v;
+  a.g1 = g1; a.ld_g1 = ld_g1; a.g2 = g2; a.ld_g2 = ld_g2; a.p1 = p1; a.p2 = p2; a.p3 = p3; a.cap = cap; a.q_scale = q_scale;
+  a.state = state; a.slot_stride = slot_stride; a.seg_q_start = seg_q_start; a.seg_slot = seg_slot; a.H = H; a.dk = dk; a.dv = dv;
+  dim3 grid(S, H, tiles);
+  cudaStream_t st = (cudaStream_t)stream;
+#define LAUNCH_SCAN(TT, KIND)                                                                                               \
+  do {                                                                                                                      \
+    if (smem > 48 * 1024) cudaFuncSetAttribute(linear_scan_kernel<TT, KIND>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+    return qv_launch(linear_scan_kernel<TT, KIND>, grid, dim3(SCAN_VT * SCAN_WARPS), smem, st, a);                          \
+  } while (0)
+  if (dt == QV_DT_F32 && kind == SCAN_GATED_MAX) LAUNCH_SCAN(float, SCAN_GATED_MAX);
+  if (dt == QV_DT_F32 && kind == SCAN_DECAY) LAUNCH_SCAN(float, SCAN_DECAY);
+  if (dt == QV_DT_BF16 && kind == SCAN_GATED_MAX) LAUNCH_SCAN(bf16, SCAN_GATED_MAX);
+  if (dt == QV_DT_BF16 && kind == SCAN_DECAY) LAUNCH_SCAN(bf16, SCAN_DECAY);
+#undef LAUNCH_SCAN
+  return QV_ERR_UNSUPPORTED;
+}
+
+// ---------------------------------------------------------------- unit norm in equal parts, weight, gate
+// y [T, width] float32 in `groups` equal parts; gate [T, width] in the compute type (row stride ld_gate).
+//   gate_first = 0:  out = y / rms_part(y) * w * sigmoid(gate)
+//   gate_first = 1:  u = y * silu(gate);  out = u / rms_part(u) * w
+// One block per (token, part).
+template <typename T>
+__global__ void __launch_bounds__(128) gated_group_norm_kernel(T* __restrict__ out, int ld_out, const float* __restrict__ y, int ld_y,
+                                                               const T* __restrict__ gate, int ld_gate, const float* __restrict__ w,
+                                                               int part, float eps, int gate_first) {
+  __shared__ float red[33];
+  pdl_wait();
+  pdl_launch_dependents();
+  const int t = blockIdx.x, g = blockIdx.y;
+  const float* yr = y + (size_t)t * ld_y + (size_t)g * part;
+  const T* gr = gate + (size_t)t * ld_gate + (size_t)g * part;
+  T* o = out + (size_t)t * ld_out + (size_t)g * part;
+  const float* wr = w + (size_t)g * part;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < part; i += blockDim.x) {
+    float v = yr[i];
+    if (gate_first) { const float z = to_f(gr[i]); v *= z / (1.0f + expf(-z)); }
+    ss += v * v;
+  }
+  const float total = block_sum(ss, red);
+  const float sc = 1.0f / sqrtf(total / (float)part + eps);
+  for (int i = threadIdx.x; i < part; i += blockDim.x) {
+    const float z = to_f(gr[i]);
+    float v = yr[i];
+    if (gate_first) v = v * (z / (1.0f + expf(-z))) * sc * wr[i];
+    else v = v * sc * wr[i] * (1.0f / (1.0f + expf(-z)));
+    o[i] = from_f<T>(v);
+  }
+}
+
+extern "C" int qv_gated_group_norm(void* out, int ld_out, const float* y, int ld_y, const void* gate, int ld_gate, const float* w,
+                                   int T, int width, int groups, float eps, int gate_first, int dt, void* stream) {
+  if (T <= 0) return 0;
+  if (groups <= 0 || width % groups || groups > 65535) return QV_ERR_UNSUPPORTED;
+  QV_DISPATCH_DT(dt, TT,
+                 return qv_launch(gated_group_norm_kernel<TT>, dim3(T, groups), dim3(128), 0, (cudaStream_t)stream, (TT*)out, ld_out, y,
+                                  ld_y, (const TT*)gate, ld_gate, w, width / groups, eps, gate_first));
+  return QV_ERR_UNSUPPORTED;
+}

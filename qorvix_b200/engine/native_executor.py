@@ -97,6 +97,8 @@ class NativeExecutor:
         from ..parts.rotary import RotaryEmbedding
         if not enabled() or model.order != list(range(len(model.blocks))) or type(model.final_norm) is not RMSNorm:
             return None
+        if getattr(model, "embedder", None) is not None or getattr(model.spec, "logit_softcap", 0.0):
+            return None
         rt = model.rt
         layers, keep, group, table = [], [], None, None
         for run, b in enumerate(model.blocks):

@@ -34,7 +34,7 @@ def build_parser() -> argparse.ArgumentParser:
     p.add_argument("--max-tokens", type=int, required=True,
                    help="most tokens live requests hold at any time (each rounded up to a multiple of 64); sizes the page pool")
     p.add_argument("--page-size", type=int, default=16, help="tokens per cache page (a multiple of 16 that divides 64)")
-    p.add_argument("--max-requests", type=int, default=8, help="request slots")
+    p.add_argument("--max-requests", type=int, default=4, help="request slots (requests live at once)")
     return p
 
 

@@ -20,7 +20,12 @@ class TextModel:
         self.spec = spec
         self.rt = rt
         source.check(spec.expected_shapes(), optional=spec.optional_tensors, ignored=getattr(spec, "ignored_tensors", ()))
-        self.embedding = source.get(spec.embedding)
+        if isinstance(spec.embedding, str):
+            self.embedder = None
+            self.embedding = source.get(spec.embedding)
+        else:                                      # an embedding part (more than one table, state of its own)
+            self.embedder = build_part("embedding", spec.embedding, source, rt)
+            self.embedding = self.embedder.weight
         self.blocks = [build_part("block", _BlockView(layer), source, rt) for layer in spec.layers]
         self.final_norm = build_part("norm", spec.final_norm, source, rt)
         self.lm_head = Linear(source.get(spec.lm_head)) if spec.lm_head is not None else Linear(self.embedding)
@@ -45,6 +50,8 @@ class TextModel:
                 src_run = last_run_of[src]
             needs.append((spec, src_run))
             last_run_of[li] = run
+        if self.embedder is not None:              # the embedding's own state comes after the runs
+            needs.append((self.embedder.cache_spec(), None))
         return needs
 
     def forward(self, ctx, cache) -> Optional[torch.Tensor]:
@@ -57,7 +64,10 @@ class TextModel:
             # every block is one the native executor knows: the whole step in one call
             return self._native.forward(ctx)
         residual = torch.empty((T, self.spec.hidden_size), device=self.rt.device, dtype=torch.float32)
-        ops.embed(residual, self.embedding, ctx.token_ids)
+        if self.embedder is not None:
+            self.embedder.forward(residual, ctx, cache.layer_view(len(self.order)))
+        else:
+            ops.embed(residual, self.embedding, ctx.token_ids)
         pending = None
         for run, li in enumerate(self.order):
             # which norm reads the stream after this block (a block that can prepares that norm's input);
@@ -68,7 +78,10 @@ class TextModel:
         if ctx.num_wanted == 0:
             return None
         h = self.final_norm.add_norm(residual, pending, rows=ctx.want_rows)
-        return self.lm_head(h, out_dtype=torch.float32)
+        logits = self.lm_head(h, out_dtype=torch.float32)
+        if self.spec.logit_softcap:
+            ops.softcap(logits, self.spec.logit_softcap)
+        return logits
 
 
 class _BlockView:

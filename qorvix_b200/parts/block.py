@@ -4,6 +4,8 @@ The residual stream is float32.  A block hands the feed-forward's output on as a
 delta, which the next norm adds in its own pass."""
 from __future__ import annotations
 
+import torch
+
 from ..csrc import ops
 from .base import Block, PreNormed
 from .registry import build_part, register_part
@@ -58,4 +60,41 @@ def _folds(norm) -> bool:
     return norm is not None and getattr(norm, "folds_into_products", False)
 
 
+class ParallelBlock(Block):
+    """x += mixer(norm_a(x)) + feed_forward(norm_b(x)): both parts read the stream as it enters the block.
+    When both norms are RMS norms of one eps their rows share the root mean square and come from one pass."""
+
+    def __init__(self, spec, source, rt):
+        self.rt = rt
+        self.mixer_norm = build_part("norm", spec.mixer_norm, source, rt)
+        self.mixer = build_part("mixer", spec.mixer, source, rt)
+        self.feed_forward = build_part("feed_forward", spec.feed_forward, source, rt)
+        self.ffn_norm = build_part("norm", spec.ffn_norm, source, rt) if self.feed_forward is not None else None
+
+    def forward(self, residual, pending, ctx, cache):
+        if isinstance(pending, PreNormed):
+            pending = None                       # the product is in the stream already
+        a, b = self.mixer_norm, self.ffn_norm
+        if b is None:
+            return residual, self.mixer.forward(a.add_norm(residual, pending), ctx, cache)
+        if _folds(a) and _folds(b) and a.eps == b.eps and a.size == b.size:
+            h1 = torch.empty((residual.shape[0], a.size), device=residual.device, dtype=self.rt.dtype)
+            h2 = torch.empty_like(h1)
+            ops.add_rmsnorm2(h1, h2, residual, pending, a.scale_weight(), b.scale_weight(), a.eps)
+        else:
+            h1 = a.add_norm(residual, pending)
+            h2 = b.add_norm(residual, None)
+        mixed = self.mixer.forward(h1, ctx, cache)
+        if getattr(self.feed_forward, "takes_addend", False):
+            return residual, self.feed_forward.forward(h2, ctx, add=mixed)
+        fed = self.feed_forward.forward(h2, ctx)
+        delta = torch.empty(residual.shape, device=residual.device, dtype=torch.float32)
+        ops.sum2(delta, mixed, fed)
+        return residual, delta
+
+    def first_norm(self):
+        return None                              # two norms read the stream: nothing for the block ahead to prepare
+
+
 register_part("block", "pre_norm", PreNormBlock)
+register_part("block", "parallel", ParallelBlock)

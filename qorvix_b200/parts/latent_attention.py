@@ -1,0 +1,53 @@
+"""Attention over a cached low-rank latent.  Per token only the normed latent c (kv_rank entries) and one
+rotated key part shared by all heads are kept, in pages; a head's unrotated keys and its values are
+W_uk c and W_uv c.  The kernels never expand them: the query is carried into the latent space
+(W_uk^T q), attention runs over the cache rows as they are, and W_uv is applied to the weighted latent
+(csrc/latent_attention.cu).  Query, down projection and gate come from one fused product."""
+from __future__ import annotations
+
+import torch
+
+from ..cache.spec import PagedRowsSpec
+from ..csrc import ops
+from .base import Mixer
+from .linear import Linear
+from .registry import build_part, register_part
+
+
+class LatentAttention(Mixer):
+    def __init__(self, spec, source, rt):
+        self.spec, self.rt = spec, rt
+        self.H, self.dn, self.dr, self.dv, self.rank = spec.num_heads, spec.head_dim, spec.rot_dim, spec.value_dim, spec.kv_rank
+        mats = [source.get(spec.q_proj), source.get(spec.kv_down), source.get(spec.gate_proj)]
+        dt = torch.float32 if any(m.dtype == torch.float32 for m in mats) else mats[0].dtype
+        self.q_off, self.kv_off = 0, mats[0].shape[0]
+        self.gate_off = self.kv_off + mats[1].shape[0]
+        self.proj = Linear(torch.cat([m.to(dt) for m in mats], dim=0))
+        del mats
+        self.kv_norm = source.get(spec.kv_norm, dtype=torch.float32)
+        self.k_up = source.get(spec.k_up)
+        self.v_up = source.get(spec.v_up).to(self.k_up.dtype)
+        self.o_proj = Linear(source.get(spec.o_proj))
+        self.position = build_part("position", spec.position, source, rt)
+        if getattr(spec.position, "pairing", "") != "interleaved" or self.position.table() is None:
+            raise ValueError("latent attention rotates neighbouring pairs from a cos/sin table: its position must be a rotary "
+                             "encoding with pairing='interleaved'")
+        self.rot = self.position.table().shape[1] * 2
+        self.window, self.scale, self.eps = int(spec.window), float(spec.scale), float(spec.eps)
+
+    def cache_spec(self):
+        return PagedRowsSpec(self.rank + self.dr, self.window)
+
+    def forward(self, x, ctx, cache):
+        H, dn, dr, dv, rank = self.H, self.dn, self.dr, self.dv, self.rank
+        bt = ctx.block_tables[cache.group]
+        proj = self.proj(x, out_dtype=self.rt.dtype)
+        ops.latent_prepare(proj, self.q_off, self.kv_off, cache.tensor, self.kv_norm, self.eps, self.position.table(), ctx, bt,
+                           H, dn, dr, rank, self.rot, cache.page_size)
+        out = torch.empty((proj.shape[0], H * dv), device=proj.device, dtype=self.rt.dtype)
+        ops.latent_attention(out, proj[:, : self.kv_off], proj[:, self.gate_off:], cache.tensor, self.k_up, self.v_up, ctx, bt,
+                             H, dn, dr, dv, rank, cache.page_size, self.window, self.scale)
+        return self.o_proj(out, out_dtype=self.rt.dtype)
+
+
+register_part("mixer", "latent_attention", LatentAttention)

@@ -1,0 +1,49 @@
+"""Routed feed-forward (mixture of experts) with an optional shared expert.  The router runs in float32;
+tokens are grouped by expert on the device, the experts' products run over the grouped rows, and one
+kernel forms the weighted sum in token order, adds the shared expert (scaled by its per-token gate) and,
+if given, the output of the part that ran beside it (csrc/moe.cu)."""
+from __future__ import annotations
+
+import torch
+
+from ..csrc import ops
+from .base import FeedForward
+from .registry import build_part, register_part
+
+
+class RoutedFeedForward(FeedForward):
+    takes_addend = True            # forward(x, ctx, add=...) returns float32 with `add` summed in
+
+    def __init__(self, spec, source, rt):
+        self.spec, self.rt = spec, rt
+        self.router = source.get(spec.router)
+        names = [spec.expert_names(e) for e in range(spec.experts)]
+        self.w_gate = torch.stack([source.get(g) for g, _, _ in names]).contiguous()      # [E, ff, d]
+        self.w_up = torch.stack([source.get(u) for _, u, _ in names]).to(self.w_gate.dtype).contiguous()
+        self.w_down = torch.stack([source.get(dn) for _, _, dn in names]).to(self.w_gate.dtype).contiguous()   # [E, d, ff]
+        self.shared = build_part("feed_forward", spec.shared, source, rt)
+        self.shared_gate = source.get(spec.shared_gate).to(self.router.dtype).reshape(-1) if spec.shared is not None else None
+
+    def forward(self, x, ctx, add=None):
+        s = self.spec
+        T, d = x.shape
+        dev = x.device
+        R = T * s.top
+        top_idx = torch.empty((T, s.top), device=dev, dtype=torch.int32)
+        top_w = torch.empty((T, s.top), device=dev, dtype=torch.float32)
+        gate = torch.empty(T, device=dev, dtype=torch.float32) if self.shared is not None else None
+        ops.moe_route(top_idx, top_w, gate, x, self.router, self.shared_gate)
+        ints = torch.empty(3 * R + 3 * ops.moe_max_tiles(R, s.experts), device=dev, dtype=torch.int32)
+        row_token, slot_row, scratch, tiles = ints[:R], ints[R: 2 * R], ints[2 * R: 3 * R], ints[3 * R:]
+        ops.moe_group(row_token, slot_row, tiles, top_idx, scratch, s.experts)
+        act = torch.empty((R, s.expert_ff), device=dev, dtype=x.dtype)
+        ops.moe_experts(True, act, x, self.w_gate, self.w_up, row_token, tiles)
+        y = torch.empty((R, d), device=dev, dtype=torch.float32)
+        ops.moe_experts(False, y, act, self.w_down, None, row_token, tiles)
+        shared = self.shared.forward(x, ctx) if self.shared is not None else None
+        delta = torch.empty((T, d), device=dev, dtype=torch.float32)
+        ops.moe_combine(delta, add, y, slot_row, top_w, shared, gate)
+        return delta
+
+
+register_part("feed_forward", "moe", RoutedFeedForward)

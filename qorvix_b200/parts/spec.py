@@ -8,8 +8,8 @@ from __future__ import annotations
 from dataclasses import dataclass, field
 from typing import Dict, List, Optional, Tuple
 
-# tensor table entries: name -> (shape, kind) with kind in {"matrix", "norm"} (how random
-# weights are drawn)
+# tensor table entries: name -> (shape, kind) with kind in {"matrix", "norm", "normal:<mean>:<std>"}
+# (how random weights are drawn)
 TensorTable = Dict[str, Tuple[Tuple[int, ...], str]]
 
 
@@ -22,6 +22,7 @@ class RotarySpec:
     theta: float
     scaling: Optional[object] = None          # config.RopeScaling or None
     kind: str = "rotary"
+    pairing: str = "split_half"               # "interleaved": entry 2i is paired with 2i+1 (mixers that rotate themselves)
 
     def tensors(self) -> TensorTable:
         return {}
@@ -83,9 +84,167 @@ class SwiGLUSpec:
 
 
 @dataclass(frozen=True)
+class BigramEmbeddingSpec:
+    """Token embedding plus a row of a second table chosen by a hash of (previous token, token):
+    (prev * mul_prev + token * mul_cur) mod buckets; a request's first token takes row `buckets`."""
+    vocab_size: int
+    hidden_size: int
+    table: str
+    pair_table: str
+    buckets: int
+    mul_prev: int
+    mul_cur: int
+    kind: str = "bigram_embedding"
+
+    def tensors(self) -> TensorTable:
+        return {self.table: ((self.vocab_size, self.hidden_size), "matrix"),
+                self.pair_table: ((self.buckets + 1, self.hidden_size), "matrix")}
+
+
+@dataclass(frozen=True)
+class LatentAttentionSpec:
+    """Causal attention whose keys and values are expanded from a cached low-rank latent; each head's
+    query and key have `head_dim` unrotated entries followed by `rot_dim` rotated ones, the rotated key
+    part being one vector shared by all heads; a sigmoid gate multiplies the heads' outputs."""
+    hidden_size: int
+    num_heads: int
+    head_dim: int                 # unrotated query/key entries per head
+    rot_dim: int                  # rotated query/key entries per head
+    value_dim: int
+    kv_rank: int
+    scale: float
+    eps: float                    # of the latent's RMS norm
+    position: object              # RotarySpec over rot_dim with interleaved pairing
+    q_proj: str
+    kv_down: str                  # [kv_rank + rot_dim, hidden]
+    kv_norm: str
+    k_up: str                     # [heads * head_dim, kv_rank]
+    v_up: str                     # [heads * value_dim, kv_rank]
+    gate_proj: str
+    o_proj: str
+    window: int = 0
+    kind: str = "latent_attention"
+
+    def tensors(self) -> TensorTable:
+        H, d = self.num_heads, self.hidden_size
+        return {self.q_proj: ((H * (self.head_dim + self.rot_dim), d), "matrix"),
+                self.kv_down: ((self.kv_rank + self.rot_dim, d), "matrix"),
+                self.kv_norm: ((self.kv_rank,), "norm"),
+                self.k_up: ((H * self.head_dim, self.kv_rank), "matrix"),
+                self.v_up: ((H * self.value_dim, self.kv_rank), "matrix"),
+                self.gate_proj: ((H * self.value_dim, d), "matrix"),
+                self.o_proj: ((d, H * self.value_dim), "matrix")}
+
+
+@dataclass(frozen=True)
+class MLSTMSpec:
+    """Matrix-memory LSTM: per head a key_dim x value_dim state with exponential input and forget gates
+    (pre-activations soft-limited to +-gate_cap) and a running maximum for stability; heads are
+    unit-normed, weighted and gated with a sigmoid before the output projection."""
+    hidden_size: int
+    num_heads: int
+    key_dim: int
+    value_dim: int
+    gate_cap: float
+    eps: float
+    q_proj: str
+    k_proj: str
+    v_proj: str
+    gate_proj: str
+    i_proj: str
+    i_bias: str
+    f_proj: str
+    f_bias: str
+    norm: str
+    o_proj: str
+    kind: str = "mlstm"
+
+    def tensors(self) -> TensorTable:
+        H, d, dk, dv = self.num_heads, self.hidden_size, self.key_dim, self.value_dim
+        return {self.q_proj: ((H * dk, d), "matrix"), self.k_proj: ((H * dk, d), "matrix"),
+                self.v_proj: ((H * dv, d), "matrix"), self.gate_proj: ((H * dv, d), "matrix"),
+                self.o_proj: ((d, H * dv), "matrix"), self.norm: ((H * dv,), "norm"),
+                self.i_proj: ((H, d), "matrix"), self.i_bias: ((H,), "normal:0:0.5"),
+                self.f_proj: ((H, d), "matrix"), self.f_bias: ((H,), "normal:3:0.5")}
+
+
+@dataclass(frozen=True)
+class Mamba2Spec:
+    """Selective state space with a scalar decay per head (state_dim x value_dim state), a short causal
+    convolution over x, B and C ahead of it and a SiLU gate followed by an RMS norm in equal parts behind."""
+    hidden_size: int
+    num_heads: int
+    value_dim: int
+    state_dim: int
+    groups: int
+    conv_taps: int
+    norm_groups: int
+    eps: float
+    in_proj: str                  # rows [z | x | B | C | dt]
+    conv_weight: str
+    conv_bias: str
+    dt_bias: str
+    a_log: str
+    skip: str
+    norm: str
+    o_proj: str
+    kind: str = "mamba2"
+
+    @property
+    def inner(self) -> int:
+        return self.num_heads * self.value_dim
+
+    @property
+    def conv_channels(self) -> int:
+        return self.inner + 2 * self.groups * self.state_dim
+
+    def tensors(self) -> TensorTable:
+        H, d = self.num_heads, self.hidden_size
+        return {self.in_proj: ((self.inner + self.conv_channels + H, d), "matrix"),
+                self.conv_weight: ((self.conv_channels, self.conv_taps), "normal:0:0.3"),
+                self.conv_bias: ((self.conv_channels,), "normal:0:0.1"),
+                self.dt_bias: ((H,), "normal:-1:0.5"), self.a_log: ((H,), "normal:0:0.5"),
+                self.skip: ((H,), "norm"), self.norm: ((self.inner,), "norm"),
+                self.o_proj: ((d, self.inner), "matrix")}
+
+
+@dataclass(frozen=True)
+class MoESpec:
+    """Routed feed-forward: `experts` gated feed-forwards of which each token uses `top`, weighted by the
+    softmax over the chosen router logits; optionally a shared gated feed-forward for every token, scaled
+    by the sigmoid of one number per token."""
+    hidden_size: int
+    experts: int
+    top: int
+    expert_ff: int
+    router: str
+    expert_prefix: str            # expert e's matrices are <prefix><e>.gate / .up / .down
+    shared: Optional[SwiGLUSpec] = None
+    shared_gate: Optional[str] = None
+    kind: str = "moe"
+
+    def expert_names(self, e: int):
+        p = f"{self.expert_prefix}{e}."
+        return p + "gate", p + "up", p + "down"
+
+    def tensors(self) -> TensorTable:
+        t: TensorTable = {self.router: ((self.experts, self.hidden_size), "matrix")}
+        for e in range(self.experts):
+            g, u, dn = self.expert_names(e)
+            t[g] = ((self.expert_ff, self.hidden_size), "matrix")
+            t[u] = ((self.expert_ff, self.hidden_size), "matrix")
+            t[dn] = ((self.hidden_size, self.expert_ff), "matrix")
+        if self.shared is not None:
+            t.update(self.shared.tensors())
+            t[self.shared_gate] = ((1, self.hidden_size), "matrix")
+        return t
+
+
+@dataclass(frozen=True)
 class LayerSpec:
     """One block: which parts and how they are arranged ('pre_norm': x += mixer(norm(x));
-    x += ffn(norm(x)), the reference's order, runtime/src/text_model.cpp:146-168)."""
+    x += ffn(norm(x)), the reference's order, runtime/src/text_model.cpp:146-168; 'parallel':
+    x += mixer(norm_a(x)) + ffn(norm_b(x)), both reading the stream as it enters)."""
     mixer: object
     feed_forward: object
     mixer_norm: object
@@ -106,7 +265,7 @@ class ModelSpec:
     architecture: str
     vocab_size: int
     hidden_size: int
-    embedding: str
+    embedding: object                         # the table's tensor name, or an embedding spec (built as a part)
     layers: List[LayerSpec]
     final_norm: object
     lm_head: Optional[str]                    # None: the head is the embedding table (tied)
@@ -114,6 +273,7 @@ class ModelSpec:
     optional_tensors: Tuple[str, ...] = ()    # may be stored but are not used (e.g. a tied head's copy)
     ignored_tensors: Tuple[str, ...] = ()     # name patterns (fnmatch) of stored buffers that are no weights
     max_position: int = 0
+    logit_softcap: float = 0.0                # > 0: logits = cap * tanh(logits / cap)
 
     def __post_init__(self):
         if self.order is None:
@@ -123,7 +283,10 @@ class ModelSpec:
                 raise ValueError(f"layer order names layer {i}, the model has {len(self.layers)}")
 
     def tensor_table(self) -> TensorTable:
-        t: TensorTable = {self.embedding: ((self.vocab_size, self.hidden_size), "matrix")}
+        if isinstance(self.embedding, str):
+            t: TensorTable = {self.embedding: ((self.vocab_size, self.hidden_size), "matrix")}
+        else:
+            t = dict(self.embedding.tensors())
         for layer in self.layers:
             t.update(layer.tensors())
         t.update(self.final_norm.tensors())

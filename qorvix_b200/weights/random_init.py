@@ -29,13 +29,16 @@ def _generator(seed: int, name: str, device) -> torch.Generator:
 
 
 def draw_tensor(name: str, shape, kind: str, seed: int, device="cpu", dtype=torch.bfloat16) -> torch.Tensor:
-    """kind: 'matrix' -> N(0, 0.02); 'norm' -> 1 + N(0, 0.1).  Drawn in float32, then rounded."""
+    """kind: 'matrix' -> N(0, 0.02); 'norm' -> 1 + N(0, 0.1); 'normal:<mean>:<std>'.  Drawn in float32, then rounded."""
     g = _generator(seed, name, torch.device(device))
     t = torch.randn(tuple(shape), generator=g, device=device, dtype=torch.float32)
     if kind == "norm":
         t = 1.0 + NORM_STD * t
     elif kind == "matrix":
         t = MATRIX_STD * t
+    elif kind.startswith("normal:"):
+        _, mean, std = kind.split(":")
+        t = float(mean) + float(std) * t
     else:
         raise ValueError(f"unknown tensor kind {kind!r}")
     return t.to(dtype)
