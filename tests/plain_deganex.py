@@ -55,7 +55,7 @@ def rotate_pairs(x, pos, dims, base):
     return out
 
 
-def latent_attention(h, W, m, eps):
+def latent_attention(h, W, m, eps, window=0):
     """Attention whose keys and values are expanded from a shared low-rank latent; one rotated
     key part is shared by all heads.  Causal, softmax over all visible keys, sigmoid output gate."""
     T = h.shape[0]
@@ -71,9 +71,10 @@ def latent_attention(h, W, m, eps):
     out = torch.zeros(T, H, dv, dtype=F64)
     for t in range(T):
         for hd in range(H):
-            s = (k_plain[: t + 1, hd] @ q_plain[t, hd] + k_rot[: t + 1] @ q_rot[t, hd]) * m["scale"]
+            lo = max(0, t - window + 1) if window else 0           # a window keeps the last `window` keys (the model itself has none)
+            s = (k_plain[lo: t + 1, hd] @ q_plain[t, hd] + k_rot[lo: t + 1] @ q_rot[t, hd]) * m["scale"]
             p = torch.softmax(s, dim=0)
-            out[t, hd] = p @ val[: t + 1, hd]
+            out[t, hd] = p @ val[lo: t + 1, hd]
     gated = out.reshape(T, H * dv) * torch.sigmoid(h @ W["g"].T)
     return gated @ W["o"].T
 
@@ -172,8 +173,11 @@ def forward(cfg, weights, tokens, keep_layers=False):
     """Logits [T, vocab] of one whole sequence (and the residual stream after every layer run)."""
     w = {k: v.to(F64) for k, v in weights.items()}
     eps = cfg["norm"]["eps"]
-    bg = cfg["embedding"]["bigram"]
-    x = embed_bigram(list(tokens), w["embed"], w["bigram"], bg["buckets"], bg["mul_prev"], bg["mul_cur"])
+    bg = (cfg.get("embedding") or {}).get("bigram")
+    if bg:
+        x = embed_bigram(list(tokens), w["embed"], w["bigram"], bg["buckets"], bg["mul_prev"], bg["mul_cur"])
+    else:
+        x = w["embed"][list(tokens)]
     streams = []
     for i, layer in enumerate(cfg["layers"]):
         p = f"l{owner(cfg['layers'], i)}."
@@ -187,6 +191,13 @@ def forward(cfg, weights, tokens, keep_layers=False):
     if cap:
         logits = cap * torch.tanh(logits / cap)
     return (logits, torch.stack(streams)) if keep_layers else logits
+
+
+def greedy(cfg, weights, prompt, n):
+    seq = list(prompt)
+    for _ in range(n):
+        seq.append(int(forward(cfg, weights, seq)[-1].argmax()))
+    return seq[len(prompt):]
 
 
 def read_model_dir(model_dir):
