@@ -114,18 +114,22 @@ __global__ void __launch_bounds__(1024) moe_group_kernel(int* __restrict__ row_t
 #define MOE_BN 64
 #define MOE_BK 16
 
-extern "C" int qv_moe_max_tiles(int R, int E) {
-  const int a = (R + MOE_BM - 1) / MOE_BM + E;
+#define MOE_TC_BM 64       // rows of a tile of the tensor-core kernel
+
+extern "C" int qv_moe_tile_rows(int tensor_cores) { return tensor_cores ? MOE_TC_BM : MOE_BM; }
+
+extern "C" int qv_moe_max_tiles(int R, int E, int bm) {
+  const int a = (R + bm - 1) / bm + E;
   return a < R ? a : R;
 }
 
 extern "C" int qv_moe_group(int* row_token, int* slot_row, int* tiles, const int* top_idx, int* rank_tmp, int T, int top, int E,
-                            void* stream) {
+                            int bm, void* stream) {
   if (T <= 0) return 0;
-  if (E > 8192) return QV_ERR_UNSUPPORTED;
+  if (E > 8192 || bm <= 0) return QV_ERR_UNSUPPORTED;
   const int R = T * top;
   return qv_launch(moe_group_kernel, dim3(1), dim3(1024), (size_t)2 * E * sizeof(int), (cudaStream_t)stream, row_token, slot_row, tiles,
-                   qv_moe_max_tiles(R, E), top_idx, rank_tmp, R, top, E, MOE_BM);
+                   qv_moe_max_tiles(R, E, bm), top_idx, rank_tmp, R, top, E, bm);
 }
 
 // Tile of 32 rows x 64 columns, 256 threads, each 2 rows x 4 columns; k in steps of 16, ascending.
@@ -206,7 +210,7 @@ __global__ void __launch_bounds__(256) moe_experts_kernel(void* __restrict__ out
 extern "C" int qv_moe_experts(int up, void* out, int ld_out, const void* a, int ld_a, const void* w1, const void* w2,
                               const int* row_token, const int* tiles, int R, int E, int N, int K, int dt, int w_dt, void* stream) {
   if (R <= 0) return 0;
-  const int max_tiles = qv_moe_max_tiles(R, E);
+  const int max_tiles = qv_moe_max_tiles(R, E, MOE_BM);
   if (max_tiles > 65535) return QV_ERR_TOO_LARGE;
   dim3 grid((N + MOE_BN - 1) / MOE_BN, max_tiles);
   cudaStream_t st = (cudaStream_t)stream;
@@ -223,6 +227,146 @@ extern "C" int qv_moe_experts(int up, void* out, int ld_out, const void* a, int 
   if (dt == QV_DT_F32 && w_dt == QV_DT_BF16) EXPERTS(float, bf16);
 #undef EXPERTS
   return QV_ERR_UNSUPPORTED;
+}
+
+// ---------------------------------------------------------------- the experts' products on the tensor cores (bfloat16)
+// Tile of 64 grouped rows x 64 columns, k in steps of 32 through a two-stage cp.async ring; four warps, each
+// 32 x 32 as mma.sync m16n8k16 with float32 accumulators; rows of A are gathered by row_token (UP) while they
+// are copied, rows past the tile's end and k past K are zero-filled.  K must be a multiple of 8.
+#define TC_BN 64
+#define TC_BK 32
+#define TC_LD (TC_BK + 8)      // padded row of a staged tile (bfloat16 elements): ldmatrix without bank conflicts
+
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem, int bytes) {
+  const uint32_t s = (uint32_t)__cvta_generic_to_shared(smem);
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(s), "l"(gmem), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void ldsm4(uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3, const void* p) {
+  const uint32_t s = (uint32_t)__cvta_generic_to_shared(p);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(s));
+}
+__device__ __forceinline__ void mma16816(float* c, const uint32_t* a, uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+template <bool UP>
+__global__ void __launch_bounds__(128) moe_experts_tc_kernel(void* __restrict__ out_, int ld_out, const bf16* __restrict__ a, int ld_a,
+                                                             const bf16* __restrict__ w1, const bf16* __restrict__ w2,
+                                                             const int* __restrict__ row_token, const int* __restrict__ tiles, int N, int K) {
+  __shared__ __align__(16) bf16 As[2][MOE_TC_BM][TC_LD];
+  __shared__ __align__(16) bf16 B1[2][TC_BN][TC_LD];
+  __shared__ __align__(16) bf16 B2[UP ? 2 : 1][UP ? TC_BN : 1][TC_LD];
+  pdl_wait();
+  pdl_launch_dependents();
+  const int e = tiles[3 * blockIdx.y];
+  if (e < 0) return;
+  const int row0 = tiles[3 * blockIdx.y + 1], rows = tiles[3 * blockIdx.y + 2];
+  const int n0 = blockIdx.x * TC_BN;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int wm = warp >> 1, wn = warp & 1;
+  const bf16* W1 = w1 + (size_t)e * N * K;
+  const bf16* W2 = UP ? w2 + (size_t)e * N * K : nullptr;
+  // each thread copies two 16-byte pieces of every staged tile: (row, piece) = (c / 4, c % 4), c = tid, tid + 128
+  const bf16* a_src[2];
+  bool a_ok[2];
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int r = (tid + i * 128) >> 2;
+    a_ok[i] = r < rows;
+    const size_t src_row = a_ok[i] ? (UP ? (size_t)row_token[row0 + r] : (size_t)(row0 + r)) : 0;
+    a_src[i] = a + src_row * ld_a;
+  }
+  auto stage = [&](int buf, int k0) {
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const int c = tid + i * 128, r = c >> 2, k = k0 + (c & 3) * 8;
+      const bool kin = k < K;
+      cp_async16(&As[buf][r][(c & 3) * 8], a_src[i] + (kin ? k : 0), (a_ok[i] && kin) ? 16 : 0);
+      const int n = n0 + r;
+      const bool ok = n < N && kin;
+      const size_t off = ok ? (size_t)n * K + k : 0;
+      cp_async16(&B1[buf][r][(c & 3) * 8], W1 + off, ok ? 16 : 0);
+      if (UP) cp_async16(&B2[buf][r][(c & 3) * 8], W2 + off, ok ? 16 : 0);
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+  float acc1[2][4][4] = {}, acc2[UP ? 2 : 1][4][4] = {};
+  const int nk = (K + TC_BK - 1) / TC_BK;
+  stage(0, 0);
+  for (int kt = 0; kt < nk; ++kt) {
+    const int buf = kt & 1;
+    if (kt + 1 < nk) {
+      stage(buf ^ 1, (kt + 1) * TC_BK);
+      asm volatile("cp.async.wait_group 1;" ::: "memory");
+    } else {
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
+    }
+    __syncthreads();
+#pragma unroll
+    for (int ks = 0; ks < TC_BK / 16; ++ks) {
+      uint32_t af[2][4];
+#pragma unroll
+      for (int mt = 0; mt < 2; ++mt)
+        ldsm4(af[mt][0], af[mt][1], af[mt][2], af[mt][3], &As[buf][wm * 32 + mt * 16 + (lane & 15)][ks * 16 + (lane >> 4) * 8]);
+#pragma unroll
+      for (int pr = 0; pr < 2; ++pr) {
+        const int n = wn * 32 + pr * 16 + (lane >> 4) * 8 + (lane & 7), k = ks * 16 + ((lane >> 3) & 1) * 8;
+        uint32_t b[4];
+        ldsm4(b[0], b[1], b[2], b[3], &B1[buf][n][k]);
+#pragma unroll
+        for (int mt = 0; mt < 2; ++mt) {
+          mma16816(acc1[mt][pr * 2], af[mt], b[0], b[1]);
+          mma16816(acc1[mt][pr * 2 + 1], af[mt], b[2], b[3]);
+        }
+        if (UP) {
+          ldsm4(b[0], b[1], b[2], b[3], &B2[buf][n][k]);
+#pragma unroll
+          for (int mt = 0; mt < 2; ++mt) {
+            mma16816(acc2[mt][pr * 2], af[mt], b[0], b[1]);
+            mma16816(acc2[mt][pr * 2 + 1], af[mt], b[2], b[3]);
+          }
+        }
+      }
+    }
+    __syncthreads();
+  }
+  // accumulator (mt, nt): rows wm*32 + mt*16 + lane/4 (+8), columns wn*32 + nt*8 + 2*(lane%4) (+1)
+#pragma unroll
+  for (int mt = 0; mt < 2; ++mt) {
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      const int r = wm * 32 + mt * 16 + (lane >> 2) + half * 8;
+      if (r >= rows) continue;
+#pragma unroll
+      for (int nt = 0; nt < 4; ++nt) {
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+          const int n = n0 + wn * 32 + nt * 8 + 2 * (lane & 3) + j;
+          if (n >= N) continue;
+          const float v = acc1[mt][nt][half * 2 + j];
+          if (UP) ((bf16*)out_)[(size_t)(row0 + r) * ld_out + n] = __float2bfloat16_rn(v / (1.0f + expf(-v)) * acc2[mt][nt][half * 2 + j]);
+          else ((float*)out_)[(size_t)(row0 + r) * ld_out + n] = v;
+        }
+      }
+    }
+  }
+}
+
+// As qv_moe_experts for bfloat16 operands, on the tensor cores; the tile table must have been made for tiles of
+// qv_moe_tile_rows(1) rows.  Refuses K that is no multiple of 8 and rows that do not start on 16 bytes.
+extern "C" int qv_moe_experts_tc(int up, void* out, int ld_out, const void* a, int ld_a, const void* w1, const void* w2,
+                                 const int* row_token, const int* tiles, int R, int E, int N, int K, void* stream) {
+  if (R <= 0) return 0;
+  if ((K & 7) || (ld_a & 7) || (((uintptr_t)a | (uintptr_t)w1 | (uintptr_t)w2) & 15)) return QV_ERR_UNSUPPORTED;
+  const int max_tiles = qv_moe_max_tiles(R, E, MOE_TC_BM);
+  if (max_tiles > 65535) return QV_ERR_TOO_LARGE;
+  dim3 grid((N + TC_BN - 1) / TC_BN, max_tiles);
+  cudaStream_t st = (cudaStream_t)stream;
+  if (up) return qv_launch(moe_experts_tc_kernel<true>, grid, dim3(128), 0, st, out, ld_out, (const bf16*)a, ld_a, (const bf16*)w1,
+                           (const bf16*)w2, row_token, tiles, N, K);
+  return qv_launch(moe_experts_tc_kernel<false>, grid, dim3(128), 0, st, out, ld_out, (const bf16*)a, ld_a, (const bf16*)w1,
+                   (const bf16*)w2, row_token, tiles, N, K);
 }
 
 // delta [T, d] float32.  mix, shared: [T, d] in the compute type or null; gate [T] float32 or null.

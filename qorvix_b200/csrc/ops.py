@@ -65,8 +65,10 @@ _ARGTYPES = {
     "qv_linear_scan": [_I, _V, _I, _V, _I, _I, _V, _I, _V, _I, _V, _I, _V, _I, _V, _V, _V, _F, _F, _V, _L, _V, _V, _I, _I, _I, _I, _I, _V],
     "qv_gated_group_norm": [_V, _I, _V, _I, _V, _I, _V, _I, _I, _I, _F, _I, _I, _V],
     "qv_moe_route": [_V, _V, _V, _V, _I, _V, _V, _I, _I, _I, _I, _I, _I, _V],
-    "qv_moe_max_tiles": [_I, _I],
-    "qv_moe_group": [_V, _V, _V, _V, _V, _I, _I, _I, _V],
+    "qv_moe_max_tiles": [_I, _I, _I],
+    "qv_moe_tile_rows": [_I],
+    "qv_moe_group": [_V, _V, _V, _V, _V, _I, _I, _I, _I, _V],
+    "qv_moe_experts_tc": [_I, _V, _I, _V, _I, _V, _V, _V, _V, _I, _I, _I, _I, _V],
     "qv_moe_experts": [_I, _V, _I, _V, _I, _V, _V, _V, _V, _I, _I, _I, _I, _I, _I, _V],
     "qv_moe_combine": [_V, _V, _V, _V, _V, _V, _V, _I, _I, _I, _I, _V],
     "qv_argmax": [_V, _V, _I, _I, _L, _V],
@@ -382,26 +384,45 @@ def moe_route(top_idx, top_w, gate_out, h, w_router, w_gate) -> None:
     _check(rc, "moe_route")
 
 
-def moe_max_tiles(rows: int, experts: int) -> int:
-    return int(_lib("moe").qv_moe_max_tiles(rows, experts))
+def moe_tile_rows(tensor_cores: bool) -> int:
+    """Rows of a tile of grouped rows: what the tile table is made for (the two experts' kernels differ)."""
+    return int(_lib("moe").qv_moe_tile_rows(1 if tensor_cores else 0))
 
 
-def moe_group(row_token, slot_row, tiles, top_idx, scratch, experts: int) -> None:
-    """Sorts the (token, choice) pairs by expert on the device; see csrc/moe.cu."""
+def moe_max_tiles(rows: int, experts: int, tile_rows: int) -> int:
+    return int(_lib("moe").qv_moe_max_tiles(rows, experts, tile_rows))
+
+
+def moe_group(row_token, slot_row, tiles, top_idx, scratch, experts: int, tile_rows: int) -> None:
+    """Sorts the (token, choice) pairs by expert on the device and lists the tiles of `tile_rows` rows; see csrc/moe.cu."""
     _need_cuda(row_token, slot_row, tiles, top_idx, scratch)
     T, top = top_idx.shape
-    rc = _lib("moe").qv_moe_group(_ptr(row_token), _ptr(slot_row), _ptr(tiles), _ptr(top_idx), _ptr(scratch), T, top, experts, _stream())
+    rc = _lib("moe").qv_moe_group(_ptr(row_token), _ptr(slot_row), _ptr(tiles), _ptr(top_idx), _ptr(scratch), T, top, experts,
+                                  tile_rows, _stream())
     _check(rc, "moe_group")
 
 
-def moe_experts(up: bool, out, a, w1, w2, row_token, tiles) -> None:
+def moe_tensor_cores(x, w_up, w_down) -> bool:
+    """Whether the experts' products of these operands run on the tensor-core kernel (bfloat16, both inner sizes
+    multiples of 8); the tile table is then made for its tiles."""
+    return (x.dtype == torch.bfloat16 and w_up.dtype == torch.bfloat16 and w_down.dtype == torch.bfloat16
+            and w_up.shape[2] % 8 == 0 and w_down.shape[2] % 8 == 0 and x.stride(0) % 8 == 0)
+
+
+def moe_experts(up: bool, out, a, w1, w2, row_token, tiles, tensor_cores: bool = False) -> None:
     """The experts' products over the grouped rows.  up: out[r] = silu(w1[e] x) * (w2[e] x) with x = a[row_token[r]];
-    else out[r] (float32) = w1[e] a[r].  w1, w2: [E, N, K]."""
+    else out[r] (float32) = w1[e] a[r].  w1, w2: [E, N, K].  tensor_cores: the tile table was made for the
+    tensor-core kernel (moe_tensor_cores said so), which then runs; else the CUDA-core kernel."""
     _need_cuda(out, a, w1, w2, row_token, tiles)
     R = row_token.numel()
     E, N, K = w1.shape
     assert w1.is_contiguous() and a.stride(1) == 1 and out.stride(1) == 1 and a.shape[1] == K and out.shape == (R, N)
     assert out.dtype == (a.dtype if up else torch.float32)
+    if tensor_cores:
+        rc = _lib("moe").qv_moe_experts_tc(1 if up else 0, _ptr(out), out.stride(0), _ptr(a), a.stride(0), _ptr(w1), _ptr(w2),
+                                           _ptr(row_token), _ptr(tiles), R, E, N, K, _stream())
+        _check(rc, "moe_experts_tc")
+        return
     rc = _lib("moe").qv_moe_experts(1 if up else 0, _ptr(out), out.stride(0), _ptr(a), a.stride(0), _ptr(w1), _ptr(w2),
                                     _ptr(row_token), _ptr(tiles), R, E, N, K, dt_code(a.dtype), dt_code(w1.dtype), _stream())
     _check(rc, "moe_experts")

@@ -33,13 +33,15 @@ class RoutedFeedForward(FeedForward):
         top_w = torch.empty((T, s.top), device=dev, dtype=torch.float32)
         gate = torch.empty(T, device=dev, dtype=torch.float32) if self.shared is not None else None
         ops.moe_route(top_idx, top_w, gate, x, self.router, self.shared_gate)
-        ints = torch.empty(3 * R + 3 * ops.moe_max_tiles(R, s.experts), device=dev, dtype=torch.int32)
+        tc = ops.moe_tensor_cores(x, self.w_up, self.w_down)
+        tile_rows = ops.moe_tile_rows(tc)
+        ints = torch.empty(3 * R + 3 * ops.moe_max_tiles(R, s.experts, tile_rows), device=dev, dtype=torch.int32)
         row_token, slot_row, scratch, tiles = ints[:R], ints[R: 2 * R], ints[2 * R: 3 * R], ints[3 * R:]
-        ops.moe_group(row_token, slot_row, tiles, top_idx, scratch, s.experts)
+        ops.moe_group(row_token, slot_row, tiles, top_idx, scratch, s.experts, tile_rows)
         act = torch.empty((R, s.expert_ff), device=dev, dtype=x.dtype)
-        ops.moe_experts(True, act, x, self.w_gate, self.w_up, row_token, tiles)
+        ops.moe_experts(True, act, x, self.w_gate, self.w_up, row_token, tiles, tc)
         y = torch.empty((R, d), device=dev, dtype=torch.float32)
-        ops.moe_experts(False, y, act, self.w_down, None, row_token, tiles)
+        ops.moe_experts(False, y, act, self.w_down, None, row_token, tiles, tc)
         shared = self.shared.forward(x, ctx) if self.shared is not None else None
         delta = torch.empty((T, d), device=dev, dtype=torch.float32)
         ops.moe_combine(delta, add, y, slot_row, top_w, shared, gate)
