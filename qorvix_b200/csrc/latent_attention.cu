@@ -208,3 +208,317 @@ extern "C" int qv_latent_attention_generic(void* out, int ld_out, const void* q,
   }
   return 0;
 }
+
+// ---------------------------------------------------------------- tensor-core path (bfloat16)
+// Three launches: (1) qv_latent_absorb carries every (token, head) query into the latent space, giving rows
+// [Wuk_h^T q_plain | q_rot] of rank + dr entries; (2) latent_attention_tc_kernel runs attention with all heads
+// sharing the cache rows as keys ([c | kr]) and as values (c): a CTA of eight warps takes 32 consecutive
+// (token, head) rows of one segment and walks its keys in blocks of 64 staged by cp.async in two buffers;
+// Q.K^T and P.V are mma.sync m16n8k16 with float32 accumulators, the softmax is float32 with a running
+// maximum; the keys of a tile may be split over several CTAs, each leaving an unnormalised partial result;
+// (3) qv_latent_expand merges the partial results, applies the head's value matrix and the gate.
+#define LT_BM 32
+#define LT_BK 64
+#define LT_WARPS 8
+
+__device__ __forceinline__ void lt_cp16(void* smem, const void* gmem, int bytes) {
+  const uint32_t s = (uint32_t)__cvta_generic_to_shared(smem);
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(s), "l"(gmem), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void lt_ldsm4(uint32_t* r, const void* p) {
+  const uint32_t s = (uint32_t)__cvta_generic_to_shared(p);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
+}
+__device__ __forceinline__ void lt_ldsm2(uint32_t* r, const void* p) {
+  const uint32_t s = (uint32_t)__cvta_generic_to_shared(p);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0,%1}, [%2];" : "=r"(r[0]), "=r"(r[1]) : "r"(s));
+}
+__device__ __forceinline__ void lt_ldsm2t(uint32_t* r, const void* p) {
+  const uint32_t s = (uint32_t)__cvta_generic_to_shared(p);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0,%1}, [%2];" : "=r"(r[0]), "=r"(r[1]) : "r"(s));
+}
+__device__ __forceinline__ void lt_mma(float* c, const uint32_t* a, const uint32_t* b) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
+}
+
+// qlat[(t * H + h)][:] = [sum_i q_plain[i] * wuk[h * dn + i][:] | q_rot]  (bfloat16)
+__global__ void __launch_bounds__(128) latent_absorb_kernel(bf16* __restrict__ qlat, const bf16* __restrict__ q, int ld_q,
+                                                            const bf16* __restrict__ wuk, int H, int dn, int dr, int rank) {
+  extern __shared__ float qp[];
+  pdl_wait();
+  pdl_launch_dependents();
+  const int t = blockIdx.x, h = blockIdx.y;
+  const bf16* qrow = q + (size_t)t * ld_q + (size_t)h * (dn + dr);
+  bf16* dst = qlat + ((size_t)t * H + h) * (rank + dr);
+  for (int i = threadIdx.x; i < dn; i += blockDim.x) qp[i] = to_f(qrow[i]);
+  for (int i = threadIdx.x; i < dr; i += blockDim.x) dst[rank + i] = qrow[dn + i];
+  __syncthreads();
+  const bf16* w = wuk + (size_t)h * dn * rank;
+  for (int r = threadIdx.x * 2; r < rank; r += blockDim.x * 2) {
+    float a0 = 0.f, a1 = 0.f;
+    for (int i = 0; i < dn; ++i) {
+      const __nv_bfloat162 wv = *(const __nv_bfloat162*)(w + (size_t)i * rank + r);
+      a0 = fmaf(qp[i], __low2float(wv), a0);
+      a1 = fmaf(qp[i], __high2float(wv), a1);
+    }
+    *(__nv_bfloat162*)(dst + r) = __floats2bfloat162_rn(a0, a1);
+  }
+}
+
+template <int NTW>
+__global__ void __launch_bounds__(LT_WARPS * 32) latent_attention_tc_kernel(
+    float* __restrict__ part_o, float* __restrict__ part_ml, const bf16* __restrict__ qlat, const bf16* __restrict__ cache,
+    const int* __restrict__ seg_q_start, const int* __restrict__ seg_pos0, const int* __restrict__ block_table, int max_blocks,
+    int H, int dr, int page, int window, float scale, int splits, int total_rows) {
+  constexpr int RANK = NTW * 64;
+  extern __shared__ __align__(16) unsigned char lt_smem[];
+  const int kw = RANK + dr, ldk = kw + 8;
+  bf16* Qs = (bf16*)lt_smem;                               // [32][ldk]
+  bf16* Ks = Qs + (size_t)LT_BM * ldk;                     // [2][64][ldk]
+  bf16* Ps = Ks + (size_t)2 * LT_BK * ldk;                 // [32][72]
+  float* st_max = (float*)(Ps + LT_BM * (LT_BK + 8));      // [8][32]
+  float* st_sum = st_max + LT_WARPS * LT_BM;               // [8][32]
+  pdl_wait();
+  pdl_launch_dependents();
+  const int s = blockIdx.y, split = blockIdx.z;
+  const int q0 = seg_q_start[s], q1 = seg_q_start[s + 1];
+  const int row_first = q0 * H + blockIdx.x * LT_BM;       // global (token, head) row of this tile's first row
+  const int rows = min(LT_BM, q1 * H - row_first);
+  if (rows <= 0) return;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int pos0 = seg_pos0[s];
+  const int pos_first = pos0 + row_first / H - q0, pos_last = pos0 + (row_first + rows - 1) / H - q0;
+  const int lo_tile = window > 0 ? max(0, pos_first - window + 1) : 0;
+  const int b_first = lo_tile / LT_BK, nb_all = pos_last / LT_BK - b_first + 1;
+  const int b_lo = b_first + (int)((long long)nb_all * split / splits), b_hi = b_first + (int)((long long)nb_all * (split + 1) / splits);
+  const int* bt = block_table + (size_t)s * max_blocks;
+  const int pieces = kw / 8;                               // 16-byte pieces of a row
+
+  auto load_keys = [&](int buf, int blk) {
+    bf16* dst = Ks + (size_t)buf * LT_BK * ldk;
+    for (int c = tid; c < LT_BK * pieces; c += LT_WARPS * 32) {
+      const int r = c / pieces, p = c - r * pieces, key = blk * LT_BK + r;
+      const bool ok = key <= pos_last;
+      const bf16* src = cache + (ok ? ((size_t)bt[key / page] * page + (size_t)(key % page)) * kw + p * 8 : 0);
+      lt_cp16(dst + (size_t)r * ldk + p * 8, src, ok ? 16 : 0);
+    }
+  };
+  for (int c = tid; c < LT_BM * pieces; c += LT_WARPS * 32) {
+    const int r = c / pieces, p = c - r * pieces;
+    const bool ok = r < rows;
+    lt_cp16(Qs + (size_t)r * ldk + p * 8, qlat + (ok ? (size_t)(row_first + r) * kw + p * 8 : 0), ok ? 16 : 0);
+  }
+  if (b_lo < b_hi) load_keys(0, b_lo);
+  asm volatile("cp.async.commit_group;" ::: "memory");
+
+  // this thread's four rows (m-tile mt, half hf): tile row mt*16 + hf*8 + lane/4, with position and window start
+  int rpos[2][2], rlo[2][2];
+#pragma unroll
+  for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+    for (int hf = 0; hf < 2; ++hf) {
+      const int r = mt * 16 + hf * 8 + (lane >> 2);
+      rpos[mt][hf] = r < rows ? pos0 + (row_first + r) / H - q0 : -1;
+      rlo[mt][hf] = window > 0 ? max(0, rpos[mt][hf] - window + 1) : 0;
+    }
+  float m_run[2][2], l_run[2][2], o[2][NTW][4];
+#pragma unroll
+  for (int mt = 0; mt < 2; ++mt) {
+#pragma unroll
+    for (int hf = 0; hf < 2; ++hf) { m_run[mt][hf] = -INFINITY; l_run[mt][hf] = 0.f; }
+#pragma unroll
+    for (int nt = 0; nt < NTW; ++nt)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) o[mt][nt][e] = 0.f;
+  }
+
+  for (int blk = b_lo; blk < b_hi; ++blk) {
+    const int buf = (blk - b_lo) & 1;
+    if (blk + 1 < b_hi) {
+      load_keys(buf ^ 1, blk + 1);
+      asm volatile("cp.async.commit_group;" ::: "memory");
+      asm volatile("cp.async.wait_group 1;" ::: "memory");
+    } else {
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
+    }
+    __syncthreads();
+    const bf16* Kb = Ks + (size_t)buf * LT_BK * ldk;
+    // scores of this warp's eight keys for all 32 rows
+    float sc[2][4] = {};
+    for (int ks = 0; ks < kw / 16; ++ks) {
+      uint32_t a[2][4], b[2];
+      lt_ldsm4(a[0], Qs + (size_t)(lane & 15) * ldk + ks * 16 + (lane >> 4) * 8);
+      lt_ldsm4(a[1], Qs + (size_t)(16 + (lane & 15)) * ldk + ks * 16 + (lane >> 4) * 8);
+      lt_ldsm2(b, Kb + (size_t)(warp * 8 + (lane & 7)) * ldk + ks * 16 + ((lane >> 3) & 1) * 8);
+      lt_mma(sc[0], a[0], b);
+      lt_mma(sc[1], a[1], b);
+    }
+    const int key0 = blk * LT_BK + warp * 8 + 2 * (lane & 3);
+#pragma unroll
+    for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+      for (int hf = 0; hf < 2; ++hf) {
+        float mx = -INFINITY;
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+          const int key = key0 + j;
+          float v = sc[mt][hf * 2 + j] * scale;
+          if (key > rpos[mt][hf] || key < rlo[mt][hf]) v = -INFINITY;
+          sc[mt][hf * 2 + j] = v;
+          mx = fmaxf(mx, v);
+        }
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+        if ((lane & 3) == 0) st_max[warp * LT_BM + mt * 16 + hf * 8 + (lane >> 2)] = mx;
+      }
+    __syncthreads();
+    float corr[2][2];
+#pragma unroll
+    for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+      for (int hf = 0; hf < 2; ++hf) {
+        const int r = mt * 16 + hf * 8 + (lane >> 2);
+        float bm = st_max[r];
+#pragma unroll
+        for (int w = 1; w < LT_WARPS; ++w) bm = fmaxf(bm, st_max[w * LT_BM + r]);
+        const float m_new = fmaxf(m_run[mt][hf], bm);
+        const float m_use = m_new == -INFINITY ? 0.f : m_new;
+        corr[mt][hf] = expf(m_run[mt][hf] - m_use);
+        m_run[mt][hf] = m_new;
+        const float p0 = expf(sc[mt][hf * 2] - m_use), p1 = expf(sc[mt][hf * 2 + 1] - m_use);
+        *(__nv_bfloat162*)(Ps + (size_t)r * (LT_BK + 8) + warp * 8 + 2 * (lane & 3)) = __floats2bfloat162_rn(p0, p1);
+        float sum = p0 + p1;
+        sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+        sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+        if ((lane & 3) == 0) st_sum[warp * LT_BM + r] = sum;
+      }
+    __syncthreads();
+#pragma unroll
+    for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+      for (int hf = 0; hf < 2; ++hf) {
+        const int r = mt * 16 + hf * 8 + (lane >> 2);
+        float sum = 0.f;
+#pragma unroll
+        for (int w = 0; w < LT_WARPS; ++w) sum += st_sum[w * LT_BM + r];
+        l_run[mt][hf] = l_run[mt][hf] * corr[mt][hf] + sum;
+#pragma unroll
+        for (int nt = 0; nt < NTW; ++nt) { o[mt][nt][hf * 2] *= corr[mt][hf]; o[mt][nt][hf * 2 + 1] *= corr[mt][hf]; }
+      }
+    // weighted latents: this warp's NTW * 8 columns
+#pragma unroll
+    for (int kk = 0; kk < LT_BK / 16; ++kk) {
+      uint32_t a[2][4];
+      lt_ldsm4(a[0], Ps + (size_t)(lane & 15) * (LT_BK + 8) + kk * 16 + (lane >> 4) * 8);
+      lt_ldsm4(a[1], Ps + (size_t)(16 + (lane & 15)) * (LT_BK + 8) + kk * 16 + (lane >> 4) * 8);
+#pragma unroll
+      for (int nt = 0; nt < NTW; ++nt) {
+        uint32_t b[2];
+        lt_ldsm2t(b, Kb + (size_t)(kk * 16 + (lane & 15)) * ldk + (warp * NTW + nt) * 8);
+        lt_mma(o[0][nt], a[0], b);
+        lt_mma(o[1][nt], a[1], b);
+      }
+    }
+    __syncthreads();
+  }
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
+#pragma unroll
+  for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+    for (int hf = 0; hf < 2; ++hf) {
+      const int r = mt * 16 + hf * 8 + (lane >> 2);
+      if (r >= rows) continue;
+      const size_t prow = (size_t)split * total_rows + row_first + r;
+      if (warp == 0 && (lane & 3) == 0) { part_ml[2 * prow] = m_run[mt][hf]; part_ml[2 * prow + 1] = l_run[mt][hf]; }
+#pragma unroll
+      for (int nt = 0; nt < NTW; ++nt)
+        *(float2*)(part_o + prow * RANK + (warp * NTW + nt) * 8 + 2 * (lane & 3)) = make_float2(o[mt][nt][hf * 2], o[mt][nt][hf * 2 + 1]);
+    }
+}
+
+// out[t, h*dv + j] = gate * sum_r wuv[h*dv + j][r] * latent[r], latent = merged partial results of (t, h)
+__global__ void __launch_bounds__(128) latent_expand_kernel(bf16* __restrict__ out, int ld_out, const bf16* __restrict__ gate, int ld_gate,
+                                                            const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                                            const bf16* __restrict__ wuv, int H, int dv, int rank, int splits, int total_rows) {
+  extern __shared__ float lat[];
+  pdl_wait();
+  pdl_launch_dependents();
+  const int t = blockIdx.x, h = blockIdx.y, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const size_t row = (size_t)t * H + h;
+  float M = -INFINITY;
+  for (int s = 0; s < splits; ++s) M = fmaxf(M, part_ml[2 * ((size_t)s * total_rows + row)]);
+  float L = 0.f;
+  for (int s = 0; s < splits; ++s) {
+    const float m = part_ml[2 * ((size_t)s * total_rows + row)];
+    if (m != -INFINITY) L += expf(m - M) * part_ml[2 * ((size_t)s * total_rows + row) + 1];
+  }
+  for (int r = threadIdx.x; r < rank; r += blockDim.x) {
+    float acc = 0.f;
+    for (int s = 0; s < splits; ++s) {
+      const float m = part_ml[2 * ((size_t)s * total_rows + row)];
+      if (m != -INFINITY) acc = fmaf(expf(m - M), part_o[((size_t)s * total_rows + row) * rank + r], acc);
+    }
+    lat[r] = acc / L;
+  }
+  __syncthreads();
+  for (int j = warp; j < dv; j += 4) {
+    const bf16* w = wuv + ((size_t)h * dv + j) * rank;
+    float acc = 0.f;
+    for (int r = lane * 2; r < rank; r += 64) {
+      const __nv_bfloat162 wv = *(const __nv_bfloat162*)(w + r);
+      acc = fmaf(__low2float(wv), lat[r], acc);
+      acc = fmaf(__high2float(wv), lat[r + 1], acc);
+    }
+    acc = warp_sum(acc);
+    if (lane == 0) {
+      if (gate) acc *= 1.0f / (1.0f + expf(-to_f(gate[(size_t)t * ld_gate + (size_t)h * dv + j])));
+      out[(size_t)t * ld_out + (size_t)h * dv + j] = __float2bfloat16_rn(acc);
+    }
+  }
+}
+
+extern "C" long long qv_latent_tc_workspace_bytes(int T, int H, int dr, int rank, int splits) {
+  const long long rows = (long long)T * H;
+  return rows * (rank + dr) * 2 + (long long)splits * rows * rank * 4 + (long long)splits * rows * 2 * 4 + 64;
+}
+
+// bfloat16 operands; rank a multiple of 64 up to 512 (not 320 or 448), dr a multiple of 16.  workspace: what
+// qv_latent_tc_workspace_bytes says, 16-byte aligned.  Refuses other sizes (the caller then takes the generic kernel).
+extern "C" int qv_latent_attention_tc(void* out, int ld_out, const void* q, int ld_q, const void* gate, int ld_gate, const void* cache,
+                                      const void* wuk, const void* wuv, const int* seg_q_start, const int* seg_pos0,
+                                      const int* block_table, int max_blocks, int T, int S, int max_q_len, int H, int dn, int dr,
+                                      int dv, int rank, int page, int window, float scale, int splits, void* workspace, void* stream) {
+  if (T <= 0) return 0;
+  if (rank % 64 || rank > 512 || dr % 16 || dr < 0 || (rank & 1) || splits < 1 || S > 65535 || splits > 65535 || H > 65535)
+    return QV_ERR_UNSUPPORTED;
+  const int ntw = rank / 64;
+  if (ntw == 5 || ntw == 7) return QV_ERR_UNSUPPORTED;
+  const int kw = rank + dr, ldk = kw + 8;
+  const size_t smem = ((size_t)LT_BM * ldk + (size_t)2 * LT_BK * ldk + (size_t)LT_BM * (LT_BK + 8)) * 2 + (size_t)2 * LT_WARPS * LT_BM * 4;
+  if (smem > 220 * 1024) return QV_ERR_UNSUPPORTED;
+  cudaStream_t st = (cudaStream_t)stream;
+  const long long rows = (long long)T * H;
+  bf16* qlat = (bf16*)workspace;
+  float* part_o = (float*)((char*)workspace + ((rows * kw * 2 + 15) / 16) * 16);
+  float* part_ml = part_o + (size_t)splits * rows * rank;
+  int rc = qv_launch(latent_absorb_kernel, dim3(T, H), dim3(128), (size_t)dn * sizeof(float), st, qlat, (const bf16*)q, ld_q,
+                     (const bf16*)wuk, H, dn, dr, rank);
+  if (rc) return rc;
+  dim3 grid(((size_t)max_q_len * H + LT_BM - 1) / LT_BM, S, splits);
+#define LT_LAUNCH(N)                                                                                                        \
+  case N:                                                                                                                   \
+    cudaFuncSetAttribute(latent_attention_tc_kernel<N>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);            \
+    rc = qv_launch(latent_attention_tc_kernel<N>, grid, dim3(LT_WARPS * 32), smem, st, part_o, part_ml, (const bf16*)qlat,  \
+                   (const bf16*)cache, seg_q_start, seg_pos0, block_table, max_blocks, H, dr, page, window, scale, splits,  \
+                   (int)rows);                                                                                              \
+    break;
+  switch (ntw) {
+    LT_LAUNCH(1) LT_LAUNCH(2) LT_LAUNCH(3) LT_LAUNCH(4) LT_LAUNCH(6) LT_LAUNCH(8)
+    default: return QV_ERR_UNSUPPORTED;
+  }
+#undef LT_LAUNCH
+  if (rc) return rc;
+  return qv_launch(latent_expand_kernel, dim3(T, H), dim3(128), (size_t)rank * sizeof(float), st, (bf16*)out, ld_out, (const bf16*)gate,
+                   ld_gate, (const float*)part_o, (const float*)part_ml, (const bf16*)wuv, H, dv, rank, splits, (int)rows);
+}

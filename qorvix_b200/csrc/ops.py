@@ -60,6 +60,8 @@ _ARGTYPES = {
     "qv_softcap": [_V, _L, _F, _V],
     "qv_latent_prepare": [_V, _I, _I, _I, _V, _V, _F, _V, _I, _V, _V, _V, _I, _I, _I, _I, _I, _I, _I, _I, _I, _V],
     "qv_latent_attention_generic": [_V, _I, _V, _I, _V, _I, _V, _V, _V, _V, _V, _V, _I, _I, _I, _I, _I, _I, _I, _I, _I, _F, _I, _I, _V],
+    "qv_latent_tc_workspace_bytes": [_I, _I, _I, _I, _I],
+    "qv_latent_attention_tc": [_V, _I, _V, _I, _V, _I, _V, _V, _V, _V, _V, _V, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _F, _I, _V, _V],
     "qv_conv_state": [_V, _I, _V, _I, _V, _V, _V, _L, _V, _V, _I, _I, _I, _I, _I, _V],
     "qv_linear_scan_state_floats": [_I, _I, _I, _I],
     "qv_linear_scan": [_I, _V, _I, _V, _I, _I, _V, _I, _V, _I, _V, _I, _V, _I, _V, _V, _V, _F, _F, _V, _L, _V, _V, _I, _I, _I, _I, _I, _V],
@@ -75,7 +77,7 @@ _ARGTYPES = {
     "qv_sample": [_V, _V, _I, _I, _L, _V, _V, _V, _V, _V, _V, _I, _V, _V, _V, _V],
 }
 _RESTYPES = {"qv_error_string": ctypes.c_char_p, "qv_packed_weight_bytes": c_longlong, "qv_gemm_bf16_split_slot_bytes": c_longlong,
-             "qv_linear_scan_state_floats": c_longlong}
+             "qv_linear_scan_state_floats": c_longlong, "qv_latent_tc_workspace_bytes": c_longlong}
 _typed_libs = {}
 
 
@@ -309,8 +311,46 @@ def latent_attention_generic(out, q, gate, cache_layer, wuk, wuv, ctx, block_tab
     _check(rc, "latent_attention_generic")
 
 
+def latent_attention_splits(ctx, H: int) -> int:
+    """Into how many slices the keys of a tile of 32 (token, head) rows are cut so that a step fills the SMs (one CTA
+    each): a function of the step's shape only (a captured step keeps it)."""
+    tiles = sum(-(-n * H // 32) for n in ctx.seg_len)
+    blocks = max(1, -(-int(ctx.max_ctx_len) // 64))
+    return max(1, min(sm_count() // max(tiles, 1), blocks))
+
+
+def latent_attention_tc(out, q, gate, cache_layer, wuk, wuv, ctx, block_table, H, dn, dr, dv, rank, page, window, scale) -> bool:
+    """Latent attention on the tensor cores (bfloat16; rank a multiple of 64 up to 512, rotated part a multiple of 16).
+    False, nothing written, for other sizes."""
+    if (q.dtype != torch.bfloat16 or wuk.dtype != torch.bfloat16 or rank % 64 or rank > 512 or rank // 64 in (5, 7) or dr % 16
+            or q.stride(0) % 2 or (gate is not None and gate.dtype != torch.bfloat16)):
+        return False
+    _need_cuda(out, q, gate, cache_layer, wuk, wuv, block_table)
+    assert q.stride(1) == 1 and out.stride(1) == 1 and out.dtype == cache_layer.dtype == torch.bfloat16
+    assert cache_layer.is_contiguous() and tuple(cache_layer.shape[1:]) == (page, rank + dr)
+    assert wuk.is_contiguous() and tuple(wuk.shape) == (H * dn, rank) and wuv.is_contiguous() and tuple(wuv.shape) == (H * dv, rank)
+    _i32(block_table, "block_table")
+    T = q.shape[0]
+    splits = latent_attention_splits(ctx, H)
+    lib = _lib("latent_attention")
+    ws = torch.empty(int(lib.qv_latent_tc_workspace_bytes(T, H, dr, rank, splits)), device=q.device, dtype=torch.uint8)
+    rc = lib.qv_latent_attention_tc(
+        _ptr(out), out.stride(0), _ptr(q), q.stride(0), _ptr(gate), gate.stride(0) if gate is not None else 0, _ptr(cache_layer),
+        _ptr(wuk), _ptr(wuv), _ptr(ctx.seg_q_start), _ptr(ctx.seg_pos0), _ptr(block_table), block_table.shape[-1], T,
+        ctx.num_segments, ctx.max_q_len, H, dn, dr, dv, rank, page, window, scale, splits, _ptr(ws), _stream())
+    if rc == -2:
+        return False
+    _check(rc, "latent_attention_tc")
+    add_launches(2)                                  # the queries' move into the latent space, the merge with the value matrices
+    return True
+
+
 def latent_attention(out, q, gate, cache_layer, wuk, wuv, ctx, block_table, H, dn, dr, dv, rank, page, window, scale) -> None:
-    """Latent attention of every token of the step with the kernel that fits the dtype and the sizes."""
+    """Latent attention of every token of the step: the tensor-core kernels for bfloat16 where they take the sizes, else
+    (and for float32) the CUDA-core kernel."""
+    if q.dtype == torch.bfloat16 and latent_attention_tc(out, q, gate, cache_layer, wuk, wuv, ctx, block_table, H, dn, dr, dv, rank,
+                                                         page, window, scale):
+        return
     latent_attention_generic(out, q, gate, cache_layer, wuk, wuv, ctx, block_table, H, dn, dr, dv, rank, page, window, scale)
 
 

@@ -1,0 +1,241 @@
+"""Prefill and decode throughput of a Deganex model at layer sizes that resemble real models, beside the Llama
+decoder at equal width, depth and active feed-forward size, and the Deganex kernels alone with their roofline
+fractions beside the Llama kernels they correspond to.
+
+    python bench.py --design deganex [--layers-per-kind 2] [--batch 8] [--ctx 1024] [--prefill-tokens 2048]
+    python -m qorvix_b200.design_bench
+
+Random bfloat16 weights; timing with CUDA events after warm-up; kernels alone are timed in captured chains over
+buffers larger than L2 (kernel_bench.timed_chain).  Figures go out as one JSON line.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import statistics
+from types import SimpleNamespace
+
+import torch
+
+from . import kernel_bench as kb
+from .csrc import ops
+
+# Layer sizes: latent attention as in 16-head models with a 512-wide latent; the matrix-memory LSTM with four wide
+# heads; the state space with 64 heads of 64 over a state of 128; 64 routed experts of which 6 serve a token, and
+# a shared expert twice as wide as a routed one.
+WIDTH, VOCAB = 2048, 32000
+ATTN = {"heads": 16, "dim": 128, "rot_dim": 64, "vdim": 128, "kv_rank": 512, "scale": 192 ** -0.5, "rot": {"base": 10000.0, "dims": 64}}
+MLSTM = {"heads": 4, "dim": 256, "vdim": 512, "gate_cap": 15.0}
+MAMBA = {"heads": 64, "vdim": 64, "state": 128, "groups": 1, "conv": 4, "norm_groups": 1}
+MOE = {"kind": "moe", "expert": {"ff": 1408}, "router": {"experts": 64, "top": 6}, "shared": {"ff": 2816}}
+
+
+def deganex_config(layers_per_kind: int) -> dict:
+    kinds = [("latent_attention", ATTN), ("mlstm", MLSTM), ("mamba2", MAMBA)]
+    layers = [{"type": k, "mixer": m, "mlp": MOE} for _ in range(layers_per_kind) for k, m in kinds]
+    return {"architecture": "Deganex", "vocab": VOCAB, "width": WIDTH, "norm": {"eps": 1e-5}, "logit_softcap": 30.0,
+            "embedding": {"bigram": {"buckets": 65521, "mul_prev": 31, "mul_cur": 17}}, "layers": layers}
+
+
+def llama_config(n_layers: int) -> dict:
+    active_ff = MOE["router"]["top"] * MOE["expert"]["ff"] + MOE["shared"]["ff"]
+    return {"architectures": ["LlamaForCausalLM"], "vocab_size": VOCAB, "hidden_size": WIDTH, "intermediate_size": active_ff,
+            "num_hidden_layers": n_layers, "num_attention_heads": 16, "num_key_value_heads": 16, "head_dim": 128,
+            "max_position_embeddings": 8192, "rms_norm_eps": 1e-5, "rope_theta": 10000.0, "tie_word_embeddings": False}
+
+
+def _runner(raw, pool_tokens, concurrent):
+    from .config import architecture_of, lookup_architecture
+    from .engine import ModelRunner
+    from .weights import random_tensors
+    cfg = lookup_architecture(architecture_of(raw)).config_from_dict(raw)
+    tensors = dict(random_tensors(cfg, seed=0, device="cuda", dtype=torch.bfloat16))
+    r = ModelRunner(config=cfg, tensors=tensors, dtype="bfloat16", max_tokens=pool_tokens, max_requests=concurrent, max_model_len=8192)
+    del tensors
+    return cfg, r
+
+
+def _tokens(vocab, n, seed):
+    return [int(t) for t in torch.randint(0, vocab, (n,), generator=torch.Generator().manual_seed(seed))]
+
+
+def model_throughput(raw, batch, ctx, prefill_tokens, steps, warmup) -> dict:
+    """Prefill of one prompt and decode of `batch` requests at `ctx` cached tokens, through the step function."""
+    from .engine import StepEntry
+    cfg, r = _runner(raw, max(prefill_tokens + 64, batch * (ctx + steps + warmup + 80)), max(batch, 1))
+    V = cfg.vocab_size
+    ms = []
+    for it in range(4):
+        p = _tokens(V, prefill_tokens, it)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        r.step([StepEntry("pre", p, [prefill_tokens - 1])], end=["pre"])
+        e1.record()
+        torch.cuda.synchronize()
+        if it >= 2:
+            ms.append(e0.elapsed_time(e1))
+    pre_ms = statistics.median(ms)
+    ids = list(range(batch))
+    for i in ids:
+        r.step([StepEntry(i, _tokens(V, ctx - 1, 100 + i), [])])
+    dec = r.decoder(ids)
+    dec.start([1] * batch)
+    for _ in range(warmup):
+        dec.step()
+    torch.cuda.synchronize()
+    n0 = ops.launch_count()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        dec.step()
+    e1.record()
+    torch.cuda.synchronize()
+    dec_ms = e0.elapsed_time(e1) / steps
+    launches = (ops.launch_count() - n0) // steps
+    dec.finish()
+    ops.check_kernel_errors()
+    out = {"prefill_tokens": prefill_tokens, "prefill_ms": round(pre_ms, 3), "prefill_tok_s": round(prefill_tokens / pre_ms * 1e3, 1),
+           "decode_batch": batch, "decode_ctx": ctx, "decode_ms_per_step": round(dec_ms, 4), "decode_tok_s": round(batch / dec_ms * 1e3, 1),
+           "launches_per_decode_step": int(launches)}
+    del r, dec
+    torch.cuda.empty_cache()
+    return out
+
+
+def _ctx(seg_lens, pos0, device="cuda"):
+    """A step context of the given segments (all state slots distinct), for kernels run alone."""
+    S, T = len(seg_lens), sum(seg_lens)
+    qs = [0]
+    for n in seg_lens:
+        qs.append(qs[-1] + n)
+    i32 = dict(dtype=torch.int32, device=device)
+    return SimpleNamespace(
+        num_segments=S, num_tokens=T, max_q_len=max(seg_lens), seg_q_start=torch.tensor(qs, **i32),
+        seg_slot=torch.arange(S, **i32), tok_seg=torch.repeat_interleave(torch.arange(S, **i32), torch.tensor(seg_lens, device=device)).to(torch.int32),
+        tok_pos=torch.cat([torch.arange(p, p + n, **i32) for p, n in zip(pos0, seg_lens)]))
+
+
+def latent_attention_case(seg_lens, ctx_len, peaks, page=16) -> dict:
+    """Latent attention of the given segments, each ending at ctx_len cached tokens (prepare excluded)."""
+    H, dn, dr, dv, rank = ATTN["heads"], ATTN["dim"], ATTN["rot_dim"], ATTN["vdim"], ATTN["kv_rank"]
+    S, T = len(seg_lens), sum(seg_lens)
+    blocks = -(-ctx_len // page)
+    row_bytes = (rank + dr) * 2
+    copies = max(2, min(8, int(2.5 * kb.L2_BYTES // (S * ctx_len * row_bytes)) + 1))
+    caches = torch.randn(copies, S * blocks + 1, page, rank + dr, device="cuda", dtype=torch.bfloat16)
+    table = torch.arange(S * blocks, dtype=torch.int32, device="cuda").view(S, blocks)
+    ctx = _ctx(seg_lens, [ctx_len - n for n in seg_lens])
+    ctx.seg_len, ctx.seg_start_pos, ctx.max_ctx_len, ctx.captured = list(seg_lens), [ctx_len - n for n in seg_lens], ctx_len, False
+    ctx.seg_pos0 = torch.tensor(ctx.seg_start_pos, dtype=torch.int32, device="cuda")
+    q = torch.randn(T, H * (dn + dr), device="cuda", dtype=torch.bfloat16) * 0.3
+    gate = torch.randn(T, H * dv, device="cuda", dtype=torch.bfloat16)
+    wuk = torch.randn(H * dn, rank, device="cuda", dtype=torch.bfloat16) * 0.05
+    wuv = torch.randn(H * dv, rank, device="cuda", dtype=torch.bfloat16) * 0.05
+    out = torch.empty(T, H * dv, device="cuda", dtype=torch.bfloat16)
+    us = kb.timed_chain(lambda i: ops.latent_attention(out, q, gate, caches[i % copies], wuk, wuv, ctx, table, H, dn, dr, dv, rank, page, 0,
+                                                       ATTN["scale"]), launches=8)
+    pairs = sum(n * (ctx_len - n) + n * (n + 1) // 2 for n in seg_lens)                 # (query, key) pairs per head
+    flops = H * pairs * (2.0 * (rank + dr) + 2.0 * rank) + T * H * 2.0 * rank * (dn + dv)
+    return kb._figures(us, S * ctx_len * row_bytes + (q.numel() + gate.numel() + out.numel()) * 2, flops, peaks)
+
+
+def scan_case(kind, seg_lens, peaks) -> dict:
+    """The recurrence of the matrix-memory LSTM ('mlstm') or the state space ('mamba2') over the given segments."""
+    S, T = len(seg_lens), sum(seg_lens)
+    ctx = _ctx(seg_lens, [0] * S)
+    if kind == "mlstm":
+        H, dk, dv, code, qg = MLSTM["heads"], MLSTM["dim"], MLSTM["vdim"], ops.SCAN_GATED_MAX, 1
+    else:
+        H, dk, dv, code, qg = MAMBA["heads"], MAMBA["state"], MAMBA["vdim"], ops.SCAN_DECAY, MAMBA["heads"] // MAMBA["groups"]
+    n_state = ops.linear_scan_state_floats(code, H, dk, dv)
+    copies = max(2, min(8, int(2.5 * kb.L2_BYTES // (S * n_state * 4)) + 1))
+    states = torch.zeros(copies, S, n_state, device="cuda", dtype=torch.float32)
+    q = torch.randn(T, (H // qg) * dk, device="cuda", dtype=torch.bfloat16) * 0.1
+    k = torch.randn(T, (H // qg) * dk, device="cuda", dtype=torch.bfloat16) * 0.1
+    v = torch.randn(T, H * dv, device="cuda", dtype=torch.bfloat16)
+    g1 = torch.randn(T, H, device="cuda", dtype=torch.float32)
+    g2 = torch.randn(T, H, device="cuda", dtype=torch.float32) + 3
+    p = torch.zeros(H, device="cuda", dtype=torch.float32)
+    y = torch.empty(T, H * dv, device="cuda", dtype=torch.float32)
+    us = kb.timed_chain(lambda i: ops.linear_scan(code, y, q, k, v, g1, g2 if kind == "mlstm" else None, p, p, p, 15.0, 1.0,
+                                                  states[i % copies], ctx, H, dk, dv, q_group=qg), launches=8)
+    nbytes = 2 * S * n_state * 4 + (q.numel() + k.numel() + v.numel()) * 2 + y.numel() * 4
+    return kb._figures(us, nbytes, 4.0 * T * H * dk * dv, peaks)
+
+
+def experts_case(T, peaks) -> dict:
+    """Both products of the routed experts for T tokens (router and grouping included, shared expert excluded)."""
+    E, top, ff, d = MOE["router"]["experts"], MOE["router"]["top"], MOE["expert"]["ff"], WIDTH
+    wbytes = E * 3 * ff * d * 2
+    copies = max(2, int(2.5 * kb.L2_BYTES // wbytes) + 1)
+    wg = [torch.randn(E, ff, d, device="cuda", dtype=torch.bfloat16) * 0.02 for _ in range(copies)]
+    wu = [torch.randn(E, ff, d, device="cuda", dtype=torch.bfloat16) * 0.02 for _ in range(copies)]
+    wd = [torch.randn(E, d, ff, device="cuda", dtype=torch.bfloat16) * 0.02 for _ in range(copies)]
+    router = torch.randn(E, d, device="cuda", dtype=torch.bfloat16)
+    x = torch.randn(T, d, device="cuda", dtype=torch.bfloat16)
+    R = T * top
+    top_idx = torch.empty(T, top, device="cuda", dtype=torch.int32)
+    top_w = torch.empty(T, top, device="cuda", dtype=torch.float32)
+    tile_rows = ops.moe_tile_rows(True)
+    ints = torch.empty(3 * R + 3 * ops.moe_max_tiles(R, E, tile_rows), device="cuda", dtype=torch.int32)
+    row_token, slot_row, scratch, tiles = ints[:R], ints[R:2 * R], ints[2 * R:3 * R], ints[3 * R:]
+    act = torch.empty(R, ff, device="cuda", dtype=torch.bfloat16)
+    y = torch.empty(R, d, device="cuda", dtype=torch.float32)
+    delta = torch.empty(T, d, device="cuda", dtype=torch.float32)
+
+    def run(i):
+        ops.moe_route(top_idx, top_w, None, x, router, None)
+        ops.moe_group(row_token, slot_row, tiles, top_idx, scratch, E, tile_rows)
+        ops.moe_experts(True, act, x, wg[i % copies], wu[i % copies], row_token, tiles, True)
+        ops.moe_experts(False, y, act, wd[i % copies], None, row_token, tiles, True)
+        ops.moe_combine(delta, None, y, slot_row, top_w, None, None)
+
+    us = kb.timed_chain(run, launches=6)
+    touched = min(E, R)                                        # experts whose weights a step must read at least
+    nbytes = touched * 3 * ff * d * 2 + T * d * 2 + R * (ff * 2 * 2 + d * 4 * 2) + T * d * 4
+    return kb._figures(us, nbytes, 2.0 * R * 3 * ff * d, peaks)
+
+
+def run(args, peaks) -> dict:
+    n_layers = 3 * args.layers_per_kind
+    res = {"deganex": model_throughput(deganex_config(args.layers_per_kind), args.batch, args.ctx, args.prefill_tokens, args.steps, args.warmup),
+           "llama_equal_size": model_throughput(llama_config(n_layers), args.batch, args.ctx, args.prefill_tokens, args.steps, args.warmup)}
+    T, B, C = args.prefill_tokens, args.batch, args.ctx
+    kernels = {
+        f"latent_attention_prefill_t{T}": latent_attention_case([T], T, peaks),
+        f"latent_attention_decode_b{B}_ctx{C}": latent_attention_case([1] * B, C, peaks),
+        f"mlstm_scan_prefill_t{T}": scan_case("mlstm", [T], peaks), f"mlstm_scan_decode_b{B}": scan_case("mlstm", [1] * B, peaks),
+        f"mamba2_scan_prefill_t{T}": scan_case("mamba2", [T], peaks), f"mamba2_scan_decode_b{B}": scan_case("mamba2", [1] * B, peaks),
+        f"experts_prefill_t{T}": experts_case(T, peaks), f"experts_decode_b{B}": experts_case(B, peaks),
+    }
+    from .config import LlamaConfig
+    like = kb.headline_kernels(LlamaConfig.from_dict(llama_config(n_layers)), B, C, T, peaks)
+    ops.check_kernel_errors()
+    res["kernels"] = kernels
+    res["llama_kernels"] = {k: v for k, v in like.items() if "attention" in k or "gate_up" in k or "down" in k}
+    return res
+
+
+def main(argv=None, peaks=None) -> int:
+    ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    ap.add_argument("--layers-per-kind", type=int, default=2)
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--ctx", type=int, default=1024)
+    ap.add_argument("--prefill-tokens", type=int, default=2048)
+    ap.add_argument("--steps", type=int, default=32)
+    ap.add_argument("--warmup", type=int, default=4)
+    args, _ = ap.parse_known_args(argv)
+    peaks = peaks or {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+    res = run(args, peaks)
+    d = res["deganex"]
+    print(json.dumps({"metric": "deganex_decode_tokens_per_s", "value": d["decode_tok_s"], "unit": "tokens/s", "n_gpus": 1, "dtype": "bf16",
+                      "data": "synthetic (random weights and tokens)", "peaks": peaks,
+                      "config": {"model": f"Deganex, width {WIDTH}, {3 * args.layers_per_kind} layers", "batch": args.batch, "ctx": args.ctx,
+                                 "prefill_tokens": args.prefill_tokens, "l2": "kernels alone rotate over buffers larger than L2"},
+                      **res}))
+    return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

@@ -62,6 +62,15 @@ CONFIG_B = config([layer(mamba(heads=2, vdim=40, state=12, groups=2, conv=2, nor
                   vocab=150, width=48, eps=1e-6, softcap=0.0, bigram=None)
 
 
+# sizes the tensor-core kernels take (latent of 64, rotated part of 16, inner sizes that are multiples of 8), sixteen
+# heads so that a tile of rows spans two tokens, and sizes that differ between the mixers
+_ATTN_C = dict(heads=16, dim=8, rot_dim=16, vdim=24, kv_rank=64, scale=0.25, base=3000.0)
+CONFIG_C = config([layer(attn(**_ATTN_C), moe(experts=6, top=2, ff=32, shared=16)), layer(mamba(heads=4, vdim=32, state=16, groups=2, conv=4, norm_groups=2), moe(experts=6, top=2, ff=32, shared=16)),
+                   layer(mlstm(heads=2, dim=16, vdim=32, gate_cap=8.0), moe(experts=6, top=2, ff=32, shared=16)),
+                   layer(attn(**_ATTN_C), moe(experts=6, top=2, ff=32, shared=16), weights_of=0)],
+                  vocab=190, width=64, eps=1e-5, softcap=12.0, bigram=(31, 3, 5))
+
+
 def _rnd(g, *shape):
     return torch.randn(*shape, generator=g)
 

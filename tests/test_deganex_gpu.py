@@ -89,6 +89,8 @@ def mixer_setup(layer, dtype, width=72, eps=2e-5, seed=1, sharp=1.0, window=0, t
 
 MIXER_CASES = [dh.attn(), dh.attn(heads=1, dim=8, rot_dim=16, vdim=36, kv_rank=24, scale=0.3, base=10000.0),
                dh.attn(heads=5, dim=16, rot_dim=4, vdim=7, kv_rank=33, scale=0.4),
+               dh.attn(heads=3, dim=24, rot_dim=16, vdim=40, kv_rank=128), dh.attn(heads=5, dim=16, rot_dim=32, vdim=8, kv_rank=192, scale=0.15),
+               dh.attn(heads=16, dim=8, rot_dim=16, vdim=8, kv_rank=64),           # sizes the tensor-core kernels take
                dh.mlstm(), dh.mlstm(heads=1, dim=33, vdim=16, gate_cap=3.0), dh.mlstm(heads=2, dim=7, vdim=70, gate_cap=15.0),
                dh.mamba(), dh.mamba(heads=2, vdim=40, state=12, groups=2, conv=2, norm_groups=1),
                dh.mamba(heads=4, vdim=16, state=36, groups=1, conv=5, norm_groups=2)]
@@ -96,8 +98,9 @@ MIXER_CASES = [dh.attn(), dh.attn(heads=1, dim=8, rot_dim=16, vdim=36, kv_rank=2
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("case", range(len(MIXER_CASES)))
-def test_each_mixer_alone_in_portions_and_token_by_token(case, dtype):
+def test_each_mixer_alone_in_portions_and_token_by_token(case, dtype, monkeypatch):
     layer = MIXER_CASES[case]
+    served = count_calls(monkeypatch, "latent_attention_tc")
     sharp = 3.0 if layer["type"] == "latent_attention" else 1.0          # peaked attention: one lost key shows
     part, cache, w = mixer_setup(layer, dtype, sharp=sharp)
     x = rnd(95, 72, seed=case + 5).to(torch.bfloat16).float()
@@ -109,13 +112,30 @@ def test_each_mixer_alone_in_portions_and_token_by_token(case, dtype):
     cache.admit("filler"); cache.release("filler")
     close(run_in_portions(part, cache, x[:60], (5,) + (1,) * 55, dtype, rid="again"), want[:60], dtype, "token by token", loose=2.0)
     cache.check_invariants()
+    m = layer["mixer"]
+    if layer["type"] == "latent_attention" and dtype == torch.bfloat16 and m["kv_rank"] % 64 == 0 and m["rot_dim"] % 16 == 0:
+        assert served["latent_attention_tc"] > 0, "the tensor-core kernels were meant to serve these sizes"
+
+
+def count_calls(monkeypatch, name):
+    from qorvix_b200.csrc import ops
+    calls = {name: 0}
+    fn = getattr(ops, name)
+
+    def counted(*a, **kw):
+        res = fn(*a, **kw)
+        calls[name] += 1 if res else 0
+        return res
+    monkeypatch.setattr(ops, name, counted)
+    return calls
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("rank", [40, 64])
 @pytest.mark.parametrize("window", [1, 5, 16, 17, 40])
-def test_latent_attention_window_edges(window, dtype):
+def test_latent_attention_window_edges(window, rank, dtype):
     """Keys just inside and just outside a window, in portions and single tokens; pages the window has passed go back."""
-    layer = dh.attn()
+    layer = dh.attn(kv_rank=rank, rot_dim=8 if rank == 40 else 16)
     part, cache, w = mixer_setup(layer, dtype, sharp=3.0, window=window)
     x = rnd(95, 72, seed=3).to(torch.bfloat16).float()
     want = plain.latent_attention(x.double(), w, layer["mixer"], 2e-5, window=window)
@@ -125,12 +145,13 @@ def test_latent_attention_window_edges(window, dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-def test_latent_attention_finds_one_far_key(dtype):
+@pytest.mark.parametrize("rank,dr", [(32, 4), (64, 16)])
+def test_latent_attention_finds_one_far_key(rank, dr, dtype):
     """One key far back among hundreds is made to stand out: input 70 feeds only a barely rotated entry of the shared
     key part and is set at position 3 alone; input 71 feeds the same entry of every head's query and is set from
     position 200 on.  Those queries must then return position 3's value row, through portions and single tokens."""
-    m = dh.attn(heads=2, dim=16, rot_dim=4, vdim=24, kv_rank=32, scale=1.0, base=1e12)
-    H, dn, dr, rank = 2, 16, 4, 32
+    m = dh.attn(heads=2, dim=16, rot_dim=dr, vdim=24, kv_rank=rank, scale=1.0, base=1e12 ** (dr / 4))
+    H, dn = 2, 16
 
     def tweak(w):
         w["dkv"][rank + 2] = 0.0
@@ -204,7 +225,7 @@ def test_bigram_embedding_alone(dtype):
 @pytest.fixture(scope="module")
 def models():
     out = {}
-    for name, cfg, sharp in (("A", dh.CONFIG_A, 2.5), ("B", dh.CONFIG_B, 2.0)):
+    for name, cfg, sharp in (("A", dh.CONFIG_A, 2.5), ("B", dh.CONFIG_B, 2.0), ("C", dh.CONFIG_C, 2.0)):
         d = dh.make_model_dir(cfg, seed=11 + len(out), sharp=sharp)
         cfg_read, weights = plain.read_model_dir(d)
         out[name] = (d, cfg_read, weights, {})
@@ -228,7 +249,7 @@ def runner(model, dtype, max_tokens=256, **kw):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B"])
+@pytest.mark.parametrize("name", ["A", "B", "C"])
 def test_whole_prompts_and_layers(models, name, dtype):
     m = models[name]
     r = runner(m, dtype)
@@ -240,7 +261,7 @@ def test_whole_prompts_and_layers(models, name, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B"])
+@pytest.mark.parametrize("name", ["A", "B", "C"])
 @pytest.mark.parametrize("graphs", [True, False])
 def test_prefill_then_long_decode(models, name, dtype, graphs):
     m = models[name]
@@ -254,7 +275,7 @@ def test_prefill_then_long_decode(models, name, dtype, graphs):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B"])
+@pytest.mark.parametrize("name", ["A", "B", "C"])
 def test_portions_of_many_sizes(models, name, dtype):
     m = models[name]
     toks = tokens(m[1]["vocab"], 120, 31)
@@ -271,7 +292,7 @@ def test_portions_of_many_sizes(models, name, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B"])
+@pytest.mark.parametrize("name", ["A", "B", "C"])
 def test_mixed_batches_with_pages_and_slots_used_again(models, name, dtype):
     """Four requests of unequal length advance in unequal portions beside one another in a pool that holds little more
     than they need; two end early and two new ones take their slots and pages.  Every row equals the request alone."""
@@ -323,7 +344,7 @@ def test_float32_and_bfloat16_do_not_depend_on_the_batch(models, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B"])
+@pytest.mark.parametrize("name", ["A", "B", "C"])
 def test_greedy_generation_through_the_scheduler(models, name, dtype):
     m = models[name]
     V = m[1]["vocab"]
