@@ -242,28 +242,87 @@ __device__ __forceinline__ void lt_mma(float* c, const uint32_t* a, const uint32
                : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
 }
 
-// qlat[(t * H + h)][:] = [sum_i q_plain[i] * wuk[h * dn + i][:] | q_rot]  (bfloat16)
-__global__ void __launch_bounds__(128) latent_absorb_kernel(bf16* __restrict__ qlat, const bf16* __restrict__ q, int ld_q,
-                                                            const bf16* __restrict__ wuk, int H, int dn, int dr, int rank) {
-  extern __shared__ float qp[];
+// Per-head products on the tensor cores: for head e, out[t, e*out_off + n] = f(sum_k a[t, e*a_off + k] * w[e][n][k]),
+// t < R, n < N; tiles of 64 tokens x 64 columns, k in steps of 32 through a two-stage cp.async ring, four warps of
+// 32 x 32 (mma.sync m16n8k16, float32 accumulators).  GATED: f multiplies by sigmoid(gate[t, e*gate_off + n]).
+// tail > 0: the `tail` entries that follow a head's K inputs are copied behind its N outputs (the rotated query part
+// rides along with the query's move into the latent space).  K a multiple of 8, rows of a on 16 bytes.
+#define HG_LD 40
+template <bool GATED>
+__global__ void __launch_bounds__(128) heads_gemm_kernel(bf16* __restrict__ out, int ld_out, int out_off, const bf16* __restrict__ a, int ld_a,
+                                                         int a_off, const bf16* __restrict__ w, const bf16* __restrict__ gate, int ld_gate,
+                                                         int gate_off, int R, int N, int K, int tail) {
+  __shared__ __align__(16) bf16 As[2][64][HG_LD];
+  __shared__ __align__(16) bf16 Bs[2][64][HG_LD];
   pdl_wait();
   pdl_launch_dependents();
-  const int t = blockIdx.x, h = blockIdx.y;
-  const bf16* qrow = q + (size_t)t * ld_q + (size_t)h * (dn + dr);
-  bf16* dst = qlat + ((size_t)t * H + h) * (rank + dr);
-  for (int i = threadIdx.x; i < dn; i += blockDim.x) qp[i] = to_f(qrow[i]);
-  for (int i = threadIdx.x; i < dr; i += blockDim.x) dst[rank + i] = qrow[dn + i];
-  __syncthreads();
-  const bf16* w = wuk + (size_t)h * dn * rank;
-  for (int r = threadIdx.x * 2; r < rank; r += blockDim.x * 2) {
-    float a0 = 0.f, a1 = 0.f;
-    for (int i = 0; i < dn; ++i) {
-      const __nv_bfloat162 wv = *(const __nv_bfloat162*)(w + (size_t)i * rank + r);
-      a0 = fmaf(qp[i], __low2float(wv), a0);
-      a1 = fmaf(qp[i], __high2float(wv), a1);
+  const int e = blockIdx.z, row0 = blockIdx.y * 64, n0 = blockIdx.x * 64;
+  const int rows = min(64, R - row0);
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, wm = warp >> 1, wn = warp & 1;
+  const bf16* A = a + (size_t)e * a_off;
+  const bf16* W = w + (size_t)e * N * K;
+  if (tail > 0 && blockIdx.x == 0)
+    for (int c = tid; c < rows * tail; c += 128) {
+      const int r = c / tail, i = c - r * tail;
+      out[(size_t)(row0 + r) * ld_out + (size_t)e * out_off + N + i] = A[(size_t)(row0 + r) * ld_a + K + i];
     }
-    *(__nv_bfloat162*)(dst + r) = __floats2bfloat162_rn(a0, a1);
+  auto stage = [&](int buf, int k0) {
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const int c = tid + i * 128, r = c >> 2, k = k0 + (c & 3) * 8;
+      const bool kin = k < K, aok = r < rows && kin, bok = n0 + r < N && kin;
+      lt_cp16(&As[buf][r][(c & 3) * 8], A + (aok ? (size_t)(row0 + r) * ld_a + k : 0), aok ? 16 : 0);
+      lt_cp16(&Bs[buf][r][(c & 3) * 8], W + (bok ? (size_t)(n0 + r) * K + k : 0), bok ? 16 : 0);
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+  float acc[2][4][4] = {};
+  const int nk = (K + 31) / 32;
+  stage(0, 0);
+  for (int kt = 0; kt < nk; ++kt) {
+    const int buf = kt & 1;
+    if (kt + 1 < nk) {
+      stage(buf ^ 1, (kt + 1) * 32);
+      asm volatile("cp.async.wait_group 1;" ::: "memory");
+    } else {
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
+    }
+    __syncthreads();
+#pragma unroll
+    for (int ks = 0; ks < 2; ++ks) {
+      uint32_t af[2][4];
+#pragma unroll
+      for (int mt = 0; mt < 2; ++mt) lt_ldsm4(af[mt], &As[buf][wm * 32 + mt * 16 + (lane & 15)][ks * 16 + (lane >> 4) * 8]);
+#pragma unroll
+      for (int pr = 0; pr < 2; ++pr) {
+        uint32_t b[4];
+        lt_ldsm4(b, &Bs[buf][wn * 32 + pr * 16 + (lane >> 4) * 8 + (lane & 7)][ks * 16 + ((lane >> 3) & 1) * 8]);
+#pragma unroll
+        for (int mt = 0; mt < 2; ++mt) {
+          lt_mma(acc[mt][pr * 2], af[mt], b);
+          lt_mma(acc[mt][pr * 2 + 1], af[mt], b + 2);
+        }
+      }
+    }
+    __syncthreads();
   }
+#pragma unroll
+  for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      const int r = wm * 32 + mt * 16 + (lane >> 2) + half * 8;
+      if (r >= rows) continue;
+#pragma unroll
+      for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+          const int n = n0 + wn * 32 + nt * 8 + 2 * (lane & 3) + j;
+          if (n >= N) continue;
+          float v = acc[mt][nt][half * 2 + j];
+          if (GATED) v *= 1.0f / (1.0f + expf(-to_f(gate[(size_t)(row0 + r) * ld_gate + (size_t)e * gate_off + n])));
+          out[(size_t)(row0 + r) * ld_out + (size_t)e * out_off + n] = __float2bfloat16_rn(v);
+        }
+    }
 }
 
 template <int NTW>
@@ -437,15 +496,12 @@ __global__ void __launch_bounds__(LT_WARPS * 32) latent_attention_tc_kernel(
     }
 }
 
-// out[t, h*dv + j] = gate * sum_r wuv[h*dv + j][r] * latent[r], latent = merged partial results of (t, h)
-__global__ void __launch_bounds__(128) latent_expand_kernel(bf16* __restrict__ out, int ld_out, const bf16* __restrict__ gate, int ld_gate,
-                                                            const float* __restrict__ part_o, const float* __restrict__ part_ml,
-                                                            const bf16* __restrict__ wuv, int H, int dv, int rank, int splits, int total_rows) {
-  extern __shared__ float lat[];
+// lat[row][:] (bfloat16) = the partial results of a (token, head) row merged: sum_s e^(m_s - M) o_s / sum_s e^(m_s - M) l_s
+__global__ void __launch_bounds__(128) latent_merge_kernel(bf16* __restrict__ lat, const float* __restrict__ part_o,
+                                                           const float* __restrict__ part_ml, int rank, int splits, int total_rows) {
   pdl_wait();
   pdl_launch_dependents();
-  const int t = blockIdx.x, h = blockIdx.y, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const size_t row = (size_t)t * H + h;
+  const size_t row = blockIdx.x;
   float M = -INFINITY;
   for (int s = 0; s < splits; ++s) M = fmaxf(M, part_ml[2 * ((size_t)s * total_rows + row)]);
   float L = 0.f;
@@ -453,45 +509,37 @@ __global__ void __launch_bounds__(128) latent_expand_kernel(bf16* __restrict__ o
     const float m = part_ml[2 * ((size_t)s * total_rows + row)];
     if (m != -INFINITY) L += expf(m - M) * part_ml[2 * ((size_t)s * total_rows + row) + 1];
   }
-  for (int r = threadIdx.x; r < rank; r += blockDim.x) {
-    float acc = 0.f;
+  const float inv = 1.0f / L;
+  for (int r = threadIdx.x * 2; r < rank; r += blockDim.x * 2) {
+    float a0 = 0.f, a1 = 0.f;
     for (int s = 0; s < splits; ++s) {
       const float m = part_ml[2 * ((size_t)s * total_rows + row)];
-      if (m != -INFINITY) acc = fmaf(expf(m - M), part_o[((size_t)s * total_rows + row) * rank + r], acc);
+      if (m == -INFINITY) continue;
+      const float w = expf(m - M);
+      const float2 v = *(const float2*)(part_o + ((size_t)s * total_rows + row) * rank + r);
+      a0 = fmaf(w, v.x, a0);
+      a1 = fmaf(w, v.y, a1);
     }
-    lat[r] = acc / L;
-  }
-  __syncthreads();
-  for (int j = warp; j < dv; j += 4) {
-    const bf16* w = wuv + ((size_t)h * dv + j) * rank;
-    float acc = 0.f;
-    for (int r = lane * 2; r < rank; r += 64) {
-      const __nv_bfloat162 wv = *(const __nv_bfloat162*)(w + r);
-      acc = fmaf(__low2float(wv), lat[r], acc);
-      acc = fmaf(__high2float(wv), lat[r + 1], acc);
-    }
-    acc = warp_sum(acc);
-    if (lane == 0) {
-      if (gate) acc *= 1.0f / (1.0f + expf(-to_f(gate[(size_t)t * ld_gate + (size_t)h * dv + j])));
-      out[(size_t)t * ld_out + (size_t)h * dv + j] = __float2bfloat16_rn(acc);
-    }
+    *(__nv_bfloat162*)(lat + row * rank + r) = __floats2bfloat162_rn(a0 * inv, a1 * inv);
   }
 }
 
 extern "C" long long qv_latent_tc_workspace_bytes(int T, int H, int dr, int rank, int splits) {
   const long long rows = (long long)T * H;
-  return rows * (rank + dr) * 2 + (long long)splits * rows * rank * 4 + (long long)splits * rows * 2 * 4 + 64;
+  return rows * (rank + dr) * 2 + (long long)splits * rows * rank * 4 + (long long)splits * rows * 2 * 4 + rows * rank * 2 + 64;
 }
 
-// bfloat16 operands; rank a multiple of 64 up to 512 (not 320 or 448), dr a multiple of 16.  workspace: what
-// qv_latent_tc_workspace_bytes says, 16-byte aligned.  Refuses other sizes (the caller then takes the generic kernel).
+// bfloat16 operands; rank a multiple of 64 up to 512 (not 320 or 448), dr a multiple of 16, dn a multiple of 8.
+// wuk_t: the heads' key matrices transposed, [H][rank][dn].  workspace: what qv_latent_tc_workspace_bytes says,
+// 16-byte aligned.  Refuses other sizes (the caller then takes the generic kernel).
 extern "C" int qv_latent_attention_tc(void* out, int ld_out, const void* q, int ld_q, const void* gate, int ld_gate, const void* cache,
-                                      const void* wuk, const void* wuv, const int* seg_q_start, const int* seg_pos0,
+                                      const void* wuk_t, const void* wuv, const int* seg_q_start, const int* seg_pos0,
                                       const int* block_table, int max_blocks, int T, int S, int max_q_len, int H, int dn, int dr,
                                       int dv, int rank, int page, int window, float scale, int splits, void* workspace, void* stream) {
   if (T <= 0) return 0;
-  if (rank % 64 || rank > 512 || dr % 16 || dr < 0 || (rank & 1) || splits < 1 || S > 65535 || splits > 65535 || H > 65535)
+  if (rank % 64 || rank > 512 || dr % 16 || dr < 0 || dn % 8 || dn <= 0 || ld_q % 8 || splits < 1 || S > 65535 || splits > 65535 || H > 65535)
     return QV_ERR_UNSUPPORTED;
+  if ((T + 63) / 64 > 65535) return QV_ERR_TOO_LARGE;
   const int ntw = rank / 64;
   if (ntw == 5 || ntw == 7) return QV_ERR_UNSUPPORTED;
   const int kw = rank + dr, ldk = kw + 8;
@@ -502,8 +550,10 @@ extern "C" int qv_latent_attention_tc(void* out, int ld_out, const void* q, int 
   bf16* qlat = (bf16*)workspace;
   float* part_o = (float*)((char*)workspace + ((rows * kw * 2 + 15) / 16) * 16);
   float* part_ml = part_o + (size_t)splits * rows * rank;
-  int rc = qv_launch(latent_absorb_kernel, dim3(T, H), dim3(128), (size_t)dn * sizeof(float), st, qlat, (const bf16*)q, ld_q,
-                     (const bf16*)wuk, H, dn, dr, rank);
+  bf16* lat = (bf16*)(part_ml + (((size_t)splits * rows * 2 + 3) / 4) * 4);
+  // the queries' move into the latent space: per head q_plain [T, dn] x Wuk_h [dn, rank], the rotated part copied behind
+  int rc = qv_launch(heads_gemm_kernel<false>, dim3((rank + 63) / 64, (T + 63) / 64, H), dim3(128), 0, st, qlat, H * kw, kw,
+                     (const bf16*)q, ld_q, dn + dr, (const bf16*)wuk_t, (const bf16*)nullptr, 0, 0, T, rank, dn, dr);
   if (rc) return rc;
   dim3 grid(((size_t)max_q_len * H + LT_BM - 1) / LT_BM, S, splits);
 #define LT_LAUNCH(N)                                                                                                        \
@@ -519,6 +569,13 @@ extern "C" int qv_latent_attention_tc(void* out, int ld_out, const void* q, int 
   }
 #undef LT_LAUNCH
   if (rc) return rc;
-  return qv_launch(latent_expand_kernel, dim3(T, H), dim3(128), (size_t)rank * sizeof(float), st, (bf16*)out, ld_out, (const bf16*)gate,
-                   ld_gate, (const float*)part_o, (const float*)part_ml, (const bf16*)wuv, H, dv, rank, splits, (int)rows);
+  rc = qv_launch(latent_merge_kernel, dim3((unsigned)rows), dim3(128), 0, st, lat, (const float*)part_o, (const float*)part_ml, rank,
+                 splits, (int)rows);
+  if (rc) return rc;
+  // the heads' value matrices and the gate: per head latent [T, rank] x Wuv_h^T [rank, dv]
+  if (gate)
+    return qv_launch(heads_gemm_kernel<true>, dim3((dv + 63) / 64, (T + 63) / 64, H), dim3(128), 0, st, (bf16*)out, ld_out, dv,
+                     (const bf16*)lat, H * rank, rank, (const bf16*)wuv, (const bf16*)gate, ld_gate, dv, T, dv, rank, 0);
+  return qv_launch(heads_gemm_kernel<false>, dim3((dv + 63) / 64, (T + 63) / 64, H), dim3(128), 0, st, (bf16*)out, ld_out, dv,
+                   (const bf16*)lat, H * rank, rank, (const bf16*)wuv, (const bf16*)nullptr, 0, 0, T, dv, rank, 0);
 }

@@ -319,16 +319,18 @@ def latent_attention_splits(ctx, H: int) -> int:
     return max(1, min(sm_count() // max(tiles, 1), blocks))
 
 
-def latent_attention_tc(out, q, gate, cache_layer, wuk, wuv, ctx, block_table, H, dn, dr, dv, rank, page, window, scale) -> bool:
-    """Latent attention on the tensor cores (bfloat16; rank a multiple of 64 up to 512, rotated part a multiple of 16).
-    False, nothing written, for other sizes."""
-    if (q.dtype != torch.bfloat16 or wuk.dtype != torch.bfloat16 or rank % 64 or rank > 512 or rank // 64 in (5, 7) or dr % 16
-            or q.stride(0) % 2 or (gate is not None and gate.dtype != torch.bfloat16)):
+def latent_attention_tc(out, q, gate, cache_layer, wuk_t, wuv, ctx, block_table, H, dn, dr, dv, rank, page, window, scale) -> bool:
+    """Latent attention on the tensor cores (bfloat16; rank a multiple of 64 up to 512, rotated part a multiple of 16,
+    unrotated part a multiple of 8).  wuk_t: the heads' key matrices transposed, [H, rank, dn].  False, nothing
+    written, for other sizes."""
+    if (q.dtype != torch.bfloat16 or wuk_t is None or wuk_t.dtype != torch.bfloat16 or wuv.dtype != torch.bfloat16 or rank % 64
+            or rank > 512 or rank // 64 in (5, 7) or dr % 16 or dn % 8 or q.stride(0) % 8
+            or (gate is not None and gate.dtype != torch.bfloat16)):
         return False
-    _need_cuda(out, q, gate, cache_layer, wuk, wuv, block_table)
+    _need_cuda(out, q, gate, cache_layer, wuk_t, wuv, block_table)
     assert q.stride(1) == 1 and out.stride(1) == 1 and out.dtype == cache_layer.dtype == torch.bfloat16
     assert cache_layer.is_contiguous() and tuple(cache_layer.shape[1:]) == (page, rank + dr)
-    assert wuk.is_contiguous() and tuple(wuk.shape) == (H * dn, rank) and wuv.is_contiguous() and tuple(wuv.shape) == (H * dv, rank)
+    assert wuk_t.is_contiguous() and tuple(wuk_t.shape) == (H, rank, dn) and wuv.is_contiguous() and tuple(wuv.shape) == (H * dv, rank)
     _i32(block_table, "block_table")
     T = q.shape[0]
     splits = latent_attention_splits(ctx, H)
@@ -336,19 +338,19 @@ def latent_attention_tc(out, q, gate, cache_layer, wuk, wuv, ctx, block_table, H
     ws = torch.empty(int(lib.qv_latent_tc_workspace_bytes(T, H, dr, rank, splits)), device=q.device, dtype=torch.uint8)
     rc = lib.qv_latent_attention_tc(
         _ptr(out), out.stride(0), _ptr(q), q.stride(0), _ptr(gate), gate.stride(0) if gate is not None else 0, _ptr(cache_layer),
-        _ptr(wuk), _ptr(wuv), _ptr(ctx.seg_q_start), _ptr(ctx.seg_pos0), _ptr(block_table), block_table.shape[-1], T,
+        _ptr(wuk_t), _ptr(wuv), _ptr(ctx.seg_q_start), _ptr(ctx.seg_pos0), _ptr(block_table), block_table.shape[-1], T,
         ctx.num_segments, ctx.max_q_len, H, dn, dr, dv, rank, page, window, scale, splits, _ptr(ws), _stream())
     if rc == -2:
         return False
     _check(rc, "latent_attention_tc")
-    add_launches(2)                                  # the queries' move into the latent space, the merge with the value matrices
+    add_launches(3)                                  # the queries' move into the latent space, the merge, the value matrices
     return True
 
 
-def latent_attention(out, q, gate, cache_layer, wuk, wuv, ctx, block_table, H, dn, dr, dv, rank, page, window, scale) -> None:
-    """Latent attention of every token of the step: the tensor-core kernels for bfloat16 where they take the sizes, else
-    (and for float32) the CUDA-core kernel."""
-    if q.dtype == torch.bfloat16 and latent_attention_tc(out, q, gate, cache_layer, wuk, wuv, ctx, block_table, H, dn, dr, dv, rank,
+def latent_attention(out, q, gate, cache_layer, wuk, wuv, ctx, block_table, H, dn, dr, dv, rank, page, window, scale, wuk_t=None) -> None:
+    """Latent attention of every token of the step: the tensor-core kernels for bfloat16 where they take the sizes (and
+    the transposed key matrices wuk_t [H, rank, dn] are given), else (and for float32) the CUDA-core kernel."""
+    if q.dtype == torch.bfloat16 and latent_attention_tc(out, q, gate, cache_layer, wuk_t, wuv, ctx, block_table, H, dn, dr, dv, rank,
                                                          page, window, scale):
         return
     latent_attention_generic(out, q, gate, cache_layer, wuk, wuv, ctx, block_table, H, dn, dr, dv, rank, page, window, scale)

@@ -187,6 +187,166 @@ __global__ void __launch_bounds__(SCAN_VT * SCAN_WARPS) linear_scan_kernel(ScanA
   }
 }
 
+// The same recurrence with the state in registers (key sizes up to 8 * RPT rows: a thread keeps RPT rows of its value
+// column) and tokens taken four at a time: their inputs are fetched together, the block meets twice per four tokens
+// instead of twice per token, and each of the first four warps sums one token's partial outputs.  Arithmetic and
+// summation order are those of linear_scan_kernel; the state's layout in memory is the same.
+#define SCAN_TB 4
+#define SCAN_CH 256      // tokens whose gates are worked out together (one a thread)
+template <typename T, int KIND, int RPT>
+__global__ void __launch_bounds__(SCAN_VT * SCAN_WARPS) linear_scan_reg_kernel(ScanArgs a) {
+  extern __shared__ float sm[];
+  pdl_wait();
+  pdl_launch_dependents();
+  const int s = blockIdx.x, h = blockIdx.y, tile = blockIdx.z;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int dk = a.dk, dv = a.dv;
+  const int tiles = (dv + SCAN_VT - 1) / SCAN_VT;
+  float* qs = sm;                                  // [TB][dk]
+  float* ks = qs + SCAN_TB * dk;                   // [TB][dk]
+  float* ns = ks + SCAN_TB * dk;                   // [dk]
+  float* red = ns + dk;                            // [TB][SCAN_WARPS][32]
+  float* sc = red + SCAN_TB * SCAN_WARPS * SCAN_VT;  // [TB]
+  float* gk = sc + SCAN_TB;                        // [SCAN_CH] keep factors of the tokens in work
+  float* gt = gk + SCAN_CH;                        // [SCAN_CH] take factors
+  float* ge = gt + SCAN_CH;                        // [SCAN_CH] exp(-m) (GATED_MAX)
+  float* gm = ge + SCAN_CH;                        // [SCAN_CH] scratch of the running maximum
+  const int q0 = a.seg_q_start[s], len = a.seg_q_start[s + 1] - q0;
+  float* st = a.state + (size_t)a.seg_slot[s] * a.slot_stride + ((size_t)h * tiles + tile) * scan_tile_floats(KIND, dk);
+  float S[RPT];
+#pragma unroll
+  for (int i = 0; i < RPT; ++i) {
+    const int k = warp + SCAN_WARPS * i;
+    S[i] = k < dk ? st[k * SCAN_VT + lane] : 0.f;
+  }
+  float m = 0.f;
+  if (KIND == SCAN_GATED_MAX) {
+    for (int i = threadIdx.x; i < dk; i += blockDim.x) ns[i] = st[dk * SCAN_VT + i];
+    m = st[dk * SCAN_VT + dk];
+  }
+  const int col = tile * SCAN_VT + lane;
+  const bool live = col < dv;
+  const T* qb = (const T*)a.q + (size_t)(h / a.q_group) * dk;
+  const T* kb = (const T*)a.k + (size_t)(h / a.q_group) * dk;
+  const T* vb = (const T*)a.v + (size_t)h * dv;
+  const float b1 = a.p1 ? a.p1[h] : 0.f, b2 = a.p2 ? a.p2[h] : 0.f, b3 = a.p3 ? a.p3[h] : 0.f;
+  const float rate = KIND == SCAN_DECAY ? expf(b2) : 0.f;
+  // Gates are worked out for 256 tokens at a time, one token a thread, and kept in shared memory: the transcendental
+  // functions then lie off the path from one token to the next.  Only the running maximum is a chain (thread 0).
+  for (int c0 = 0; c0 < len; c0 += SCAN_CH) {
+    const int nch = len - c0 < SCAN_CH ? len - c0 : SCAN_CH;
+    __syncthreads();                         // the gates of the last 256 tokens have been used
+    if ((int)threadIdx.x < nch) {
+      const size_t t = (size_t)(q0 + c0 + threadIdx.x);
+      if (KIND == SCAN_GATED_MAX) {
+        const float zf = a.cap * tanhf((a.g2[t * a.ld_g2 + h] + b2) / a.cap);
+        gk[threadIdx.x] = fminf(zf, 0.f) - log1pf(expf(-fabsf(zf)));          // log forget gate
+        gt[threadIdx.x] = a.cap * tanhf((a.g1[t * a.ld_g1 + h] + b1) / a.cap);  // log input gate
+      } else {
+        const float z = a.g1[t * a.ld_g1 + h] + b1;
+        const float dt = z > 20.f ? z : log1pf(expf(z));
+        gk[threadIdx.x] = expf(-rate * dt);
+        gt[threadIdx.x] = dt;
+      }
+    }
+    if (KIND == SCAN_GATED_MAX) {
+      __syncthreads();
+      if (threadIdx.x == 0) {
+        float mm = m;
+        for (int j = 0; j < nch; ++j) {
+          const float m_new = fmaxf(gk[j] + mm, gt[j]);
+          gm[j] = mm;                          // the maximum before this token
+          ge[j] = m_new;                       // and after it
+          mm = m_new;
+        }
+      }
+      __syncthreads();
+      m = ge[nch - 1];
+      __syncthreads();                       // everyone has the maximum before its place is used for exp(-m)
+      if ((int)threadIdx.x < nch) {
+        const float lf = gk[threadIdx.x], li = gt[threadIdx.x], mp = gm[threadIdx.x], mc = ge[threadIdx.x];
+        gk[threadIdx.x] = expf(lf + mp - mc);
+        gt[threadIdx.x] = expf(li - mc);
+        ge[threadIdx.x] = expf(-mc);
+      }
+    }
+    __syncthreads();
+  for (int j0 = c0; j0 < c0 + nch; j0 += SCAN_TB) {
+    const int nb = c0 + nch - j0 < SCAN_TB ? c0 + nch - j0 : SCAN_TB;
+    const size_t t0 = (size_t)(q0 + j0);
+    for (int c = threadIdx.x; c < nb * dk; c += blockDim.x) {
+      const int tt = c / dk, i = c - tt * dk;
+      qs[c] = to_f(qb[(t0 + tt) * a.ld_q + i]) * a.q_scale;
+      ks[c] = to_f(kb[(t0 + tt) * a.ld_k + i]);
+    }
+    float vv[SCAN_TB], keep[SCAN_TB], take[SCAN_TB], mt[SCAN_TB];
+#pragma unroll
+    for (int tt = 0; tt < SCAN_TB; ++tt) {
+      vv[tt] = 0.f; keep[tt] = 1.f; take[tt] = 0.f; mt[tt] = 1.f;
+      if (tt < nb) {
+        vv[tt] = live ? to_f(vb[(t0 + tt) * a.ld_v + col]) : 0.f;
+        keep[tt] = gk[j0 - c0 + tt];
+        take[tt] = gt[j0 - c0 + tt];
+        if (KIND == SCAN_GATED_MAX) mt[tt] = ge[j0 - c0 + tt];          // exp(-m) after the token
+      }
+    }
+    __syncthreads();                       // the four tokens' q and k are in place; red and sc of the last four have been read
+    if (KIND == SCAN_GATED_MAX && warp == 0) {
+      for (int tt = 0; tt < nb; ++tt) {
+        float dot = 0.f;
+        for (int i = lane; i < dk; i += 32) {
+          const float n = keep[tt] * ns[i] + take[tt] * ks[tt * dk + i];
+          ns[i] = n;
+          dot = fmaf(n, qs[tt * dk + i], dot);
+        }
+        dot = warp_sum(dot);
+        if (lane == 0) sc[tt] = dot;
+      }
+    }
+#pragma unroll
+    for (int tt = 0; tt < SCAN_TB; ++tt) {
+      if (tt < nb) {
+        float acc = 0.f;
+        const float tv = take[tt] * vv[tt];
+#pragma unroll
+        for (int i = 0; i < RPT; ++i) {
+          const int k = warp + SCAN_WARPS * i;
+          if (k < dk) {
+            S[i] = fmaf(keep[tt], S[i], tv * ks[tt * dk + k]);
+            acc = fmaf(S[i], qs[tt * dk + k], acc);
+          }
+        }
+        red[(tt * SCAN_WARPS + warp) * SCAN_VT + lane] = acc;
+      }
+    }
+    __syncthreads();
+    if (warp < nb && live) {
+      const int tt = warp;
+      float y = 0.f;
+#pragma unroll
+      for (int w = 0; w < SCAN_WARPS; ++w) y += red[(tt * SCAN_WARPS + w) * SCAN_VT + lane];
+      // vv and mt of token tt, which this thread holds at a compile-time index only: pick without indexing registers
+      float v_tt = vv[0], m_tt = mt[0];
+#pragma unroll
+      for (int x = 1; x < SCAN_TB; ++x) if (x == tt) { v_tt = vv[x]; m_tt = mt[x]; }
+      if (KIND == SCAN_GATED_MAX) y = y / (fmaxf(fabsf(sc[tt]), m_tt) + 1e-6f);
+      else y = fmaf(b3, v_tt, y);
+      a.out[(t0 + tt) * a.ld_out + (size_t)h * dv + col] = y;
+    }
+  }
+  }
+  __syncthreads();
+#pragma unroll
+  for (int i = 0; i < RPT; ++i) {
+    const int k = warp + SCAN_WARPS * i;
+    if (k < dk) st[k * SCAN_VT + lane] = S[i];
+  }
+  if (KIND == SCAN_GATED_MAX) {
+    for (int i = threadIdx.x; i < dk; i += blockDim.x) st[dk * SCAN_VT + i] = ns[i];
+    if (threadIdx.x == 0) st[dk * SCAN_VT + dk] = m;
+  }
+}
+
 extern "C" long long qv_linear_scan_state_floats(int kind, int H, int dk, int dv) {
   return (long long)H * ((dv + SCAN_VT - 1) / SCAN_VT) * scan_tile_floats(kind, dk);
 }
@@ -207,6 +367,25 @@ extern "C" int qv_linear_scan(int kind, float* out, int ld_out, const void* q, i
   a.state = state; a.slot_stride = slot_stride; a.seg_q_start = seg_q_start; a.seg_slot = seg_slot; a.H = H; a.dk = dk; a.dv = dv;
   dim3 grid(S, H, tiles);
   cudaStream_t st = (cudaStream_t)stream;
+  if (dk <= 8 * 32) {                      // the state fits the registers
+    const size_t smem_r = ((size_t)(2 * SCAN_TB + 1) * dk + SCAN_TB * SCAN_WARPS * SCAN_VT + SCAN_TB + 4 * SCAN_CH) * sizeof(float);
+    const int rpt = dk <= 32 ? 4 : dk <= 64 ? 8 : dk <= 128 ? 16 : 32;
+#define LAUNCH_REG(TT, KIND, RPT) return qv_launch(linear_scan_reg_kernel<TT, KIND, RPT>, grid, dim3(SCAN_VT * SCAN_WARPS), smem_r, st, a)
+#define LAUNCH_REG_RPT(TT, KIND)                  \
+  do {                                            \
+    if (rpt == 4) LAUNCH_REG(TT, KIND, 4);        \
+    if (rpt == 8) LAUNCH_REG(TT, KIND, 8);        \
+    if (rpt == 16) LAUNCH_REG(TT, KIND, 16);      \
+    LAUNCH_REG(TT, KIND, 32);                     \
+  } while (0)
+    if (dt == QV_DT_F32 && kind == SCAN_GATED_MAX) LAUNCH_REG_RPT(float, SCAN_GATED_MAX);
+    if (dt == QV_DT_F32 && kind == SCAN_DECAY) LAUNCH_REG_RPT(float, SCAN_DECAY);
+    if (dt == QV_DT_BF16 && kind == SCAN_GATED_MAX) LAUNCH_REG_RPT(bf16, SCAN_GATED_MAX);
+    if (dt == QV_DT_BF16 && kind == SCAN_DECAY) LAUNCH_REG_RPT(bf16, SCAN_DECAY);
+#undef LAUNCH_REG_RPT
+#undef LAUNCH_REG
+    return QV_ERR_UNSUPPORTED;
+  }
 #define LAUNCH_SCAN(TT, KIND)                                                                                               \
   do {                                                                                                                      \
     if (smem > 48 * 1024) cudaFuncSetAttribute(linear_scan_kernel<TT, KIND>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \

@@ -132,9 +132,10 @@ def latent_attention_case(seg_lens, ctx_len, peaks, page=16) -> dict:
     gate = torch.randn(T, H * dv, device="cuda", dtype=torch.bfloat16)
     wuk = torch.randn(H * dn, rank, device="cuda", dtype=torch.bfloat16) * 0.05
     wuv = torch.randn(H * dv, rank, device="cuda", dtype=torch.bfloat16) * 0.05
+    wuk_t = wuk.view(H, dn, rank).transpose(1, 2).contiguous()
     out = torch.empty(T, H * dv, device="cuda", dtype=torch.bfloat16)
     us = kb.timed_chain(lambda i: ops.latent_attention(out, q, gate, caches[i % copies], wuk, wuv, ctx, table, H, dn, dr, dv, rank, page, 0,
-                                                       ATTN["scale"]), launches=8)
+                                                       ATTN["scale"], wuk_t=wuk_t), launches=8)
     pairs = sum(n * (ctx_len - n) + n * (n + 1) // 2 for n in seg_lens)                 # (query, key) pairs per head
     flops = H * pairs * (2.0 * (rank + dr) + 2.0 * rank) + T * H * 2.0 * rank * (dn + dv)
     return kb._figures(us, S * ctx_len * row_bytes + (q.numel() + gate.numel() + out.numel()) * 2, flops, peaks)

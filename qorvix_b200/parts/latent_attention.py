@@ -22,11 +22,19 @@ class LatentAttention(Mixer):
         dt = torch.float32 if any(m.dtype == torch.float32 for m in mats) else mats[0].dtype
         self.q_off, self.kv_off = 0, mats[0].shape[0]
         self.gate_off = self.kv_off + mats[1].shape[0]
+        rows = sum(m.shape[0] for m in mats)
+        if dt == torch.bfloat16 and rows % 8:
+            # rows of zeros behind the last matrix: every token's row of the fused product then starts on 16 bytes,
+            # which the tensor-core kernels that read q and the gate out of it ask for
+            mats.append(torch.zeros((-rows) % 8, mats[0].shape[1], device=mats[0].device, dtype=dt))
         self.proj = Linear(torch.cat([m.to(dt) for m in mats], dim=0))
         del mats
         self.kv_norm = source.get(spec.kv_norm, dtype=torch.float32)
         self.k_up = source.get(spec.k_up)
         self.v_up = source.get(spec.v_up).to(self.k_up.dtype)
+        # the tensor-core kernels read each head's key matrix with the latent index outermost
+        self.k_up_t = (self.k_up.view(self.H, self.dn, self.rank).transpose(1, 2).contiguous()
+                       if self.k_up.dtype == torch.bfloat16 else None)
         self.o_proj = Linear(source.get(spec.o_proj))
         self.position = build_part("position", spec.position, source, rt)
         if getattr(spec.position, "pairing", "") != "interleaved" or self.position.table() is None:
@@ -45,8 +53,8 @@ class LatentAttention(Mixer):
         ops.latent_prepare(proj, self.q_off, self.kv_off, cache.tensor, self.kv_norm, self.eps, self.position.table(), ctx, bt,
                            H, dn, dr, rank, self.rot, cache.page_size)
         out = torch.empty((proj.shape[0], H * dv), device=proj.device, dtype=self.rt.dtype)
-        ops.latent_attention(out, proj[:, : self.kv_off], proj[:, self.gate_off:], cache.tensor, self.k_up, self.v_up, ctx, bt,
-                             H, dn, dr, dv, rank, cache.page_size, self.window, self.scale)
+        ops.latent_attention(out, proj[:, : self.kv_off], proj[:, self.gate_off: self.gate_off + H * dv], cache.tensor, self.k_up, self.v_up, ctx, bt,
+                             H, dn, dr, dv, rank, cache.page_size, self.window, self.scale, wuk_t=self.k_up_t)
         return self.o_proj(out, out_dtype=self.rt.dtype)
 
 

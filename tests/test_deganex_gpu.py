@@ -89,7 +89,7 @@ def mixer_setup(layer, dtype, width=72, eps=2e-5, seed=1, sharp=1.0, window=0, t
 
 MIXER_CASES = [dh.attn(), dh.attn(heads=1, dim=8, rot_dim=16, vdim=36, kv_rank=24, scale=0.3, base=10000.0),
                dh.attn(heads=5, dim=16, rot_dim=4, vdim=7, kv_rank=33, scale=0.4),
-               dh.attn(heads=3, dim=24, rot_dim=16, vdim=40, kv_rank=128), dh.attn(heads=5, dim=16, rot_dim=32, vdim=8, kv_rank=192, scale=0.15),
+               dh.attn(heads=3, dim=24, rot_dim=16, vdim=40, kv_rank=128), dh.attn(heads=5, dim=16, rot_dim=32, vdim=9, kv_rank=192, scale=0.15),
                dh.attn(heads=16, dim=8, rot_dim=16, vdim=8, kv_rank=64),           # sizes the tensor-core kernels take
                dh.mlstm(), dh.mlstm(heads=1, dim=33, vdim=16, gate_cap=3.0), dh.mlstm(heads=2, dim=7, vdim=70, gate_cap=15.0),
                dh.mamba(), dh.mamba(heads=2, vdim=40, state=12, groups=2, conv=2, norm_groups=1),
@@ -113,7 +113,7 @@ def test_each_mixer_alone_in_portions_and_token_by_token(case, dtype, monkeypatc
     close(run_in_portions(part, cache, x[:60], (5,) + (1,) * 55, dtype, rid="again"), want[:60], dtype, "token by token", loose=2.0)
     cache.check_invariants()
     m = layer["mixer"]
-    if layer["type"] == "latent_attention" and dtype == torch.bfloat16 and m["kv_rank"] % 64 == 0 and m["rot_dim"] % 16 == 0:
+    if layer["type"] == "latent_attention" and dtype == torch.bfloat16 and m["kv_rank"] % 64 == 0 and m["rot_dim"] % 16 == 0 and m["dim"] % 8 == 0:
         assert served["latent_attention_tc"] > 0, "the tensor-core kernels were meant to serve these sizes"
 
 
