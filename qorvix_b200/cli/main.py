@@ -115,6 +115,9 @@ def cmd_gpu_check(args) -> int:
         print("usage: qorvix gpu-check <model_dir> [--tokens 1,2,3 | --random-prompt N]", file=sys.stderr)
         return 1
     cfg = load_config(args[1])
+    if cfg.architecture != "LlamaForCausalLM":
+        print(f"gpu-check: the plain C++ model it compares with knows the Llama decoder only, not '{cfg.architecture}'", file=sys.stderr)
+        return 1
     prompt = _prompt_from(args, cfg.vocab_size) or _prompt_from(args + ["--random-prompt", "32"], cfg.vocab_size)
     want = RefModel(args[1]).logits(prompt).astype(np.float64)
     scale = max(float(np.abs(want).max()), 1e-30)

@@ -14,19 +14,53 @@
 //                 in float32, choices summed in the order the router ranked them.
 #include "common.cuh"
 
+#define ROUTE_WARPS 8
 template <typename T, typename TW>
-__global__ void __launch_bounds__(128) moe_route_kernel(int* __restrict__ top_idx, float* __restrict__ top_w, float* __restrict__ gate_out,
+__global__ void __launch_bounds__(ROUTE_WARPS * 32) moe_route_kernel(int* __restrict__ top_idx, float* __restrict__ top_w, float* __restrict__ gate_out,
                                                         const T* __restrict__ h, int ld_h, const TW* __restrict__ wr,
                                                         const TW* __restrict__ wg, int d, int E, int top) {
-  extern __shared__ float logit[];           // E floats
+  extern __shared__ float logit[];           // E floats, then the token's d inputs
   pdl_wait();
   pdl_launch_dependents();
   const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  float* xs = logit + E;
   const T* x = h + (size_t)t * ld_h;
-  for (int e = warp; e < E + (wg ? 1 : 0); e += 4) {
+  for (int i = threadIdx.x; i < d; i += blockDim.x) xs[i] = to_f(x[i]);
+  __syncthreads();
+  for (int e = warp; e < E + (wg ? 1 : 0); e += ROUTE_WARPS) {
     const TW* w = e < E ? wr + (size_t)e * d : wg;
+    // 16-byte loads, eight in flight per lane, where the rows allow; the order of the sum depends on d only
     float acc = 0.f;
-    for (int i = lane; i < d; i += 32) acc = fmaf(to_f(w[i]), to_f(x[i]), acc);
+    constexpr int VEC = 16 / (int)sizeof(TW);
+    int i = 0;
+    if ((d % VEC) == 0 && (((uintptr_t)w) & 15) == 0) {
+      for (i = lane * VEC; i + 7 * 32 * VEC < d; i += 8 * 32 * VEC) {
+        uint4 wv[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) wv[u] = *(const uint4*)(w + i + u * 32 * VEC);
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          const TW* p = (const TW*)&wv[u];
+#pragma unroll
+          for (int k = 0; k < VEC; ++k) acc = fmaf(to_f(p[k]), xs[i + u * 32 * VEC + k], acc);
+        }
+      }
+      for (; i < d; i += 32 * VEC) {
+        const uint4 wv = *(const uint4*)(w + i);
+        const TW* p = (const TW*)&wv;
+#pragma unroll
+        for (int k = 0; k < VEC; ++k) acc = fmaf(to_f(p[k]), xs[i + k], acc);
+      }
+    } else {
+      for (i = lane; i + 7 * 32 < d; i += 8 * 32) {
+        float wv[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) wv[u] = to_f(w[i + u * 32]);
+#pragma unroll
+        for (int u = 0; u < 8; ++u) acc = fmaf(wv[u], xs[i + u * 32], acc);
+      }
+      for (; i < d; i += 32) acc = fmaf(to_f(w[i]), xs[i], acc);
+    }
     acc = warp_sum(acc);
     if (lane == 0) {
       if (e < E) logit[e] = acc;
@@ -53,9 +87,9 @@ __global__ void __launch_bounds__(128) moe_route_kernel(int* __restrict__ top_id
     const float p = expf(best - first);         // the first choice is the largest: exponents are <= 0
     denom += p;
     if (lane == 0) {
-      top_idx[(size_t)t * top + j] = bi;
+      top_idx[(size_t)t * top + j] = bi < E ? bi : 0;          // (not-a-number logits: still an expert that exists)
       top_w[(size_t)t * top + j] = p;
-      logit[bi] = -INFINITY;
+      if (bi < E) logit[bi] = -INFINITY;
     }
     __syncwarp();
   }
@@ -67,8 +101,9 @@ extern "C" int qv_moe_route(int* top_idx, float* top_w, float* gate_out, const v
   if (T <= 0) return 0;
   if (E <= 0 || top <= 0 || top > E || E > 8192) return QV_ERR_UNSUPPORTED;
   cudaStream_t st = (cudaStream_t)stream;
-  const size_t smem = (size_t)E * sizeof(float);
-#define ROUTE(TT, TW) return qv_launch(moe_route_kernel<TT, TW>, dim3(T), dim3(128), smem, st, top_idx, top_w, gate_out, (const TT*)h, ld_h, (const TW*)wr, (const TW*)wg, d, E, top)
+  const size_t smem = (size_t)(E + d) * sizeof(float);
+  if (smem > 48 * 1024) return QV_ERR_TOO_LARGE;
+#define ROUTE(TT, TW) return qv_launch(moe_route_kernel<TT, TW>, dim3(T), dim3(ROUTE_WARPS * 32), smem, st, top_idx, top_w, gate_out, (const TT*)h, ld_h, (const TW*)wr, (const TW*)wg, d, E, top)
   if (dt == QV_DT_F32 && w_dt == QV_DT_F32) ROUTE(float, float);
   if (dt == QV_DT_BF16 && w_dt == QV_DT_BF16) ROUTE(bf16, bf16);
   if (dt == QV_DT_BF16 && w_dt == QV_DT_F32) ROUTE(bf16, float);
@@ -230,12 +265,10 @@ extern "C" int qv_moe_experts(int up, void* out, int ld_out, const void* a, int 
 }
 
 // ---------------------------------------------------------------- the experts' products on the tensor cores (bfloat16)
-// Tile of 64 grouped rows x 64 columns, k in steps of 32 through a two-stage cp.async ring; four warps, each
+// Tile of 64 grouped rows x 64 columns, k in steps of BK through a cp.async ring of STAGES buffers; four warps, each
 // 32 x 32 as mma.sync m16n8k16 with float32 accumulators; rows of A are gathered by row_token (UP) while they
 // are copied, rows past the tile's end and k past K are zero-filled.  K must be a multiple of 8.
 #define TC_BN 64
-#define TC_BK 32
-#define TC_LD (TC_BK + 8)      // padded row of a staged tile (bfloat16 elements): ldmatrix without bank conflicts
 
 __device__ __forceinline__ void cp_async16(void* smem, const void* gmem, int bytes) {
   const uint32_t s = (uint32_t)__cvta_generic_to_shared(smem);
@@ -250,13 +283,17 @@ __device__ __forceinline__ void mma16816(float* c, const uint32_t* a, uint32_t b
                : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
-template <bool UP>
+template <bool UP, int BK, int STAGES>
 __global__ void __launch_bounds__(128) moe_experts_tc_kernel(void* __restrict__ out_, int ld_out, const bf16* __restrict__ a, int ld_a,
                                                              const bf16* __restrict__ w1, const bf16* __restrict__ w2,
                                                              const int* __restrict__ row_token, const int* __restrict__ tiles, int N, int K) {
-  __shared__ __align__(16) bf16 As[2][MOE_TC_BM][TC_LD];
-  __shared__ __align__(16) bf16 B1[2][TC_BN][TC_LD];
-  __shared__ __align__(16) bf16 B2[UP ? 2 : 1][UP ? TC_BN : 1][TC_LD];
+  constexpr int LD = BK + 8;                 // padded row of a staged tile: ldmatrix without bank conflicts
+  constexpr int PIECES = BK / 8;             // 16-byte pieces of a row
+  constexpr int TILE = 64 * LD;              // elements of one staged 64-row tile
+  extern __shared__ __align__(16) unsigned char moe_smem[];
+  bf16* As = (bf16*)moe_smem;                // [STAGES][64][LD]
+  bf16* B1 = As + STAGES * TILE;             // [STAGES][64][LD]
+  bf16* B2 = B1 + STAGES * TILE;             // [STAGES][64][LD] (UP)
   pdl_wait();
   pdl_launch_dependents();
   const int e = tiles[3 * blockIdx.y];
@@ -265,62 +302,55 @@ __global__ void __launch_bounds__(128) moe_experts_tc_kernel(void* __restrict__ 
   const int n0 = blockIdx.x * TC_BN;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int wm = warp >> 1, wn = warp & 1;
-  const bf16* W1 = w1 + (size_t)e * N * K;
-  const bf16* W2 = UP ? w2 + (size_t)e * N * K : nullptr;
-  // each thread copies two 16-byte pieces of every staged tile: (row, piece) = (c / 4, c % 4), c = tid, tid + 128
-  const bf16* a_src[2];
-  bool a_ok[2];
-#pragma unroll
-  for (int i = 0; i < 2; ++i) {
-    const int r = (tid + i * 128) >> 2;
-    a_ok[i] = r < rows;
-    const size_t src_row = a_ok[i] ? (UP ? (size_t)row_token[row0 + r] : (size_t)(row0 + r)) : 0;
-    a_src[i] = a + src_row * ld_a;
-  }
+  // weights are packed: [expert][N/64][K/64] tiles of 64 rows x 64 k, each 8 KB contiguous (zero-padded at the edges)
+  static_assert(BK == 64, "a stage is one packed tile");
+  const int NT = (N + 63) / 64, KT = (K + 63) / 64;
+  const bf16* W1 = w1 + ((size_t)e * NT + blockIdx.x) * KT * 4096;
+  const bf16* W2 = UP ? w2 + ((size_t)e * NT + blockIdx.x) * KT * 4096 : nullptr;
   auto stage = [&](int buf, int k0) {
-#pragma unroll
-    for (int i = 0; i < 2; ++i) {
-      const int c = tid + i * 128, r = c >> 2, k = k0 + (c & 3) * 8;
-      const bool kin = k < K;
-      cp_async16(&As[buf][r][(c & 3) * 8], a_src[i] + (kin ? k : 0), (a_ok[i] && kin) ? 16 : 0);
-      const int n = n0 + r;
-      const bool ok = n < N && kin;
-      const size_t off = ok ? (size_t)n * K + k : 0;
-      cp_async16(&B1[buf][r][(c & 3) * 8], W1 + off, ok ? 16 : 0);
-      if (UP) cp_async16(&B2[buf][r][(c & 3) * 8], W2 + off, ok ? 16 : 0);
+    if (k0 < K) {
+      const size_t tile_off = (size_t)(k0 / 64) * 4096;
+      for (int c = tid; c < 64 * PIECES; c += 128) {
+        const int r = c / PIECES, pc = c - r * PIECES, k = k0 + pc * 8;
+        const bool kin = k < K, aok = r < rows && kin;
+        const size_t src_row = aok ? (UP ? (size_t)row_token[row0 + r] : (size_t)(row0 + r)) : 0;
+        cp_async16(As + buf * TILE + r * LD + pc * 8, a + src_row * ld_a + (kin ? k : 0), aok ? 16 : 0);
+        cp_async16(B1 + buf * TILE + r * LD + pc * 8, W1 + tile_off + c * 8, 16);
+        if (UP) cp_async16(B2 + buf * TILE + r * LD + pc * 8, W2 + tile_off + c * 8, 16);
+      }
     }
-    asm volatile("cp.async.commit_group;" ::: "memory");
+    asm volatile("cp.async.commit_group;" ::: "memory");      // one group a stage, empty past the end, so the counts below hold
   };
   float acc1[2][4][4] = {}, acc2[UP ? 2 : 1][4][4] = {};
-  const int nk = (K + TC_BK - 1) / TC_BK;
-  stage(0, 0);
-  for (int kt = 0; kt < nk; ++kt) {
-    const int buf = kt & 1;
-    if (kt + 1 < nk) {
-      stage(buf ^ 1, (kt + 1) * TC_BK);
-      asm volatile("cp.async.wait_group 1;" ::: "memory");
-    } else {
-      asm volatile("cp.async.wait_group 0;" ::: "memory");
-    }
-    __syncthreads();
+  const int nk = (K + BK - 1) / BK;
 #pragma unroll
-    for (int ks = 0; ks < TC_BK / 16; ++ks) {
+  for (int st = 0; st < STAGES - 1; ++st) stage(st, st * BK);
+  for (int kt = 0; kt < nk; ++kt) {
+    const int buf = kt % STAGES;
+    asm volatile("cp.async.wait_group %0;" ::"n"(STAGES - 2) : "memory");
+    __syncthreads();                         // stage kt has landed for everyone; the buffer refilled next was read a round ago
+    stage((kt + STAGES - 1) % STAGES, (kt + STAGES - 1) * BK);
+    const bf16* Ab = As + buf * TILE;
+    const bf16* B1b = B1 + buf * TILE;
+    const bf16* B2b = B2 + buf * TILE;
+#pragma unroll
+    for (int ks = 0; ks < BK / 16; ++ks) {
       uint32_t af[2][4];
 #pragma unroll
       for (int mt = 0; mt < 2; ++mt)
-        ldsm4(af[mt][0], af[mt][1], af[mt][2], af[mt][3], &As[buf][wm * 32 + mt * 16 + (lane & 15)][ks * 16 + (lane >> 4) * 8]);
+        ldsm4(af[mt][0], af[mt][1], af[mt][2], af[mt][3], Ab + (wm * 32 + mt * 16 + (lane & 15)) * LD + ks * 16 + (lane >> 4) * 8);
 #pragma unroll
       for (int pr = 0; pr < 2; ++pr) {
         const int n = wn * 32 + pr * 16 + (lane >> 4) * 8 + (lane & 7), k = ks * 16 + ((lane >> 3) & 1) * 8;
         uint32_t b[4];
-        ldsm4(b[0], b[1], b[2], b[3], &B1[buf][n][k]);
+        ldsm4(b[0], b[1], b[2], b[3], B1b + n * LD + k);
 #pragma unroll
         for (int mt = 0; mt < 2; ++mt) {
           mma16816(acc1[mt][pr * 2], af[mt], b[0], b[1]);
           mma16816(acc1[mt][pr * 2 + 1], af[mt], b[2], b[3]);
         }
         if (UP) {
-          ldsm4(b[0], b[1], b[2], b[3], &B2[buf][n][k]);
+          ldsm4(b[0], b[1], b[2], b[3], B2b + n * LD + k);
 #pragma unroll
           for (int mt = 0; mt < 2; ++mt) {
             mma16816(acc2[mt][pr * 2], af[mt], b[0], b[1]);
@@ -329,8 +359,8 @@ __global__ void __launch_bounds__(128) moe_experts_tc_kernel(void* __restrict__ 
         }
       }
     }
-    __syncthreads();
   }
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
   // accumulator (mt, nt): rows wm*32 + mt*16 + lane/4 (+8), columns wn*32 + nt*8 + 2*(lane%4) (+1)
 #pragma unroll
   for (int mt = 0; mt < 2; ++mt) {
@@ -353,19 +383,29 @@ __global__ void __launch_bounds__(128) moe_experts_tc_kernel(void* __restrict__ 
   }
 }
 
-// As qv_moe_experts for bfloat16 operands, on the tensor cores; the tile table must have been made for tiles of
-// qv_moe_tile_rows(1) rows.  Refuses K that is no multiple of 8 and rows that do not start on 16 bytes.
+// As qv_moe_experts for bfloat16 operands, on the tensor cores, with the experts' matrices packed in tiles of 64 x 64
+// ([E][ceil(N/64)][ceil(K/64)][64][64], zero-padded: what a stage copies is 8 KB in one piece, which memory delivers
+// several times faster than 64 rows that lie a whole matrix row apart).  The tile table must have been made for tiles
+// of qv_moe_tile_rows(1) rows.  Refuses rows of `a` that do not start on 16 bytes.
 extern "C" int qv_moe_experts_tc(int up, void* out, int ld_out, const void* a, int ld_a, const void* w1, const void* w2,
                                  const int* row_token, const int* tiles, int R, int E, int N, int K, void* stream) {
   if (R <= 0) return 0;
-  if ((K & 7) || (ld_a & 7) || (((uintptr_t)a | (uintptr_t)w1 | (uintptr_t)w2) & 15)) return QV_ERR_UNSUPPORTED;
+  if ((ld_a & 7) || (((uintptr_t)a | (uintptr_t)w1 | (uintptr_t)w2) & 15)) return QV_ERR_UNSUPPORTED;
   const int max_tiles = qv_moe_max_tiles(R, E, MOE_TC_BM);
   if (max_tiles > 65535) return QV_ERR_TOO_LARGE;
   dim3 grid((N + TC_BN - 1) / TC_BN, max_tiles);
   cudaStream_t st = (cudaStream_t)stream;
-  if (up) return qv_launch(moe_experts_tc_kernel<true>, grid, dim3(128), 0, st, out, ld_out, (const bf16*)a, ld_a, (const bf16*)w1,
-                           (const bf16*)w2, row_token, tiles, N, K);
-  return qv_launch(moe_experts_tc_kernel<false>, grid, dim3(128), 0, st, out, ld_out, (const bf16*)a, ld_a, (const bf16*)w1,
+  // k in steps of 64 through three stages: a row of a weight tile is then a whole 128-byte line and two stages of
+  // copies are in flight while one is multiplied
+  constexpr int BK = 64, STAGES = 3;
+  const size_t smem = (size_t)STAGES * 64 * (BK + 8) * 2 * (up ? 3 : 2);
+  if (up) {
+    cudaFuncSetAttribute(moe_experts_tc_kernel<true, BK, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    return qv_launch(moe_experts_tc_kernel<true, BK, STAGES>, grid, dim3(128), smem, st, out, ld_out, (const bf16*)a, ld_a, (const bf16*)w1,
+                     (const bf16*)w2, row_token, tiles, N, K);
+  }
+  cudaFuncSetAttribute(moe_experts_tc_kernel<false, BK, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  return qv_launch(moe_experts_tc_kernel<false, BK, STAGES>, grid, dim3(128), smem, st, out, ld_out, (const bf16*)a, ld_a, (const bf16*)w1,
                    (const bf16*)w2, row_token, tiles, N, K);
 }
 
@@ -378,7 +418,7 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(float* __restrict__ de
   pdl_launch_dependents();
   const int t = blockIdx.x;
   const float g = gate ? gate[t] : 1.f;
-  for (int i = threadIdx.x; i < d; i += blockDim.x) {
+  for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < d; i += gridDim.y * blockDim.x) {
     float routed = 0.f;
     for (int j = 0; j < top; ++j) routed = fmaf(top_w[(size_t)t * top + j], y[(size_t)slot_row[(size_t)t * top + j] * d + i], routed);
     float v = routed;
@@ -392,7 +432,7 @@ extern "C" int qv_moe_combine(float* delta, const void* mix, const float* y, con
                               const void* shared, const float* gate, int T, int d, int top, int dt, void* stream) {
   if (T <= 0) return 0;
   QV_DISPATCH_DT(dt, TT,
-                 return qv_launch(moe_combine_kernel<TT>, dim3(T), dim3(256), 0, (cudaStream_t)stream, delta, (const TT*)mix, y, slot_row,
+                 return qv_launch(moe_combine_kernel<TT>, dim3(T, T < 256 ? (d + 255) / 256 : 1), dim3(256), 0, (cudaStream_t)stream, delta, (const TT*)mix, y, slot_row,
                                   top_w, (const TT*)shared, gate, d, top));
   return QV_ERR_UNSUPPORTED;
 }

@@ -444,27 +444,40 @@ def moe_group(row_token, slot_row, tiles, top_idx, scratch, experts: int, tile_r
     _check(rc, "moe_group")
 
 
-def moe_tensor_cores(x, w_up, w_down) -> bool:
-    """Whether the experts' products of these operands run on the tensor-core kernel (bfloat16, both inner sizes
-    multiples of 8); the tile table is then made for its tiles."""
-    return (x.dtype == torch.bfloat16 and w_up.dtype == torch.bfloat16 and w_down.dtype == torch.bfloat16
-            and w_up.shape[2] % 8 == 0 and w_down.shape[2] % 8 == 0 and x.stride(0) % 8 == 0)
+def moe_pack_experts(w: torch.Tensor) -> torch.Tensor:
+    """Experts' matrices [E, N, K] (bfloat16) as tiles of 64 rows x 64 k, [E, ceil(N/64), ceil(K/64), 64, 64],
+    zero-padded at the edges: the layout the tensor-core kernel copies a stage from in one piece."""
+    E, N, K = w.shape
+    Np, Kp = -(-N // 64) * 64, -(-K // 64) * 64
+    if (Np, Kp) != (N, K):
+        w = torch.nn.functional.pad(w, (0, Kp - K, 0, Np - N))
+    return w.view(E, Np // 64, 64, Kp // 64, 64).permute(0, 1, 3, 2, 4).contiguous()
 
 
-def moe_experts(up: bool, out, a, w1, w2, row_token, tiles, tensor_cores: bool = False) -> None:
-    """The experts' products over the grouped rows.  up: out[r] = silu(w1[e] x) * (w2[e] x) with x = a[row_token[r]];
-    else out[r] (float32) = w1[e] a[r].  w1, w2: [E, N, K].  tensor_cores: the tile table was made for the
-    tensor-core kernel (moe_tensor_cores said so), which then runs; else the CUDA-core kernel."""
+def moe_experts_tc(up: bool, out, a, p1, p2, row_token, tiles) -> None:
+    """The experts' products on the tensor cores (bfloat16).  p1, p2: matrices packed by moe_pack_experts; the sizes
+    follow from out [R, N] and a [., K]; the tile table was made for tiles of moe_tile_rows(True) rows."""
+    _need_cuda(out, a, p1, p2, row_token, tiles)
+    R, N = out.shape
+    K = a.shape[1]
+    E = p1.shape[0]
+    assert a.dtype == p1.dtype == torch.bfloat16 and a.stride(1) == 1 and out.stride(1) == 1 and a.stride(0) % 8 == 0
+    assert p1.is_contiguous() and tuple(p1.shape[1:]) == (-(-N // 64), -(-K // 64), 64, 64) and R == row_token.numel()
+    assert out.dtype == (torch.bfloat16 if up else torch.float32)
+    rc = _lib("moe").qv_moe_experts_tc(1 if up else 0, _ptr(out), out.stride(0), _ptr(a), a.stride(0), _ptr(p1), _ptr(p2),
+                                       _ptr(row_token), _ptr(tiles), R, E, N, K, _stream())
+    _check(rc, "moe_experts_tc")
+
+
+def moe_experts(up: bool, out, a, w1, w2, row_token, tiles) -> None:
+    """The experts' products over the grouped rows on the CUDA cores (float32 multiply-adds, k ascending).
+    up: out[r] = silu(w1[e] x) * (w2[e] x) with x = a[row_token[r]]; else out[r] (float32) = w1[e] a[r].
+    w1, w2: [E, N, K]; the tile table was made for tiles of moe_tile_rows(False) rows."""
     _need_cuda(out, a, w1, w2, row_token, tiles)
     R = row_token.numel()
     E, N, K = w1.shape
     assert w1.is_contiguous() and a.stride(1) == 1 and out.stride(1) == 1 and a.shape[1] == K and out.shape == (R, N)
     assert out.dtype == (a.dtype if up else torch.float32)
-    if tensor_cores:
-        rc = _lib("moe").qv_moe_experts_tc(1 if up else 0, _ptr(out), out.stride(0), _ptr(a), a.stride(0), _ptr(w1), _ptr(w2),
-                                           _ptr(row_token), _ptr(tiles), R, E, N, K, _stream())
-        _check(rc, "moe_experts_tc")
-        return
     rc = _lib("moe").qv_moe_experts(1 if up else 0, _ptr(out), out.stride(0), _ptr(a), a.stride(0), _ptr(w1), _ptr(w2),
                                     _ptr(row_token), _ptr(tiles), R, E, N, K, dt_code(a.dtype), dt_code(w1.dtype), _stream())
     _check(rc, "moe_experts")

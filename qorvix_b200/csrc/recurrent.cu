@@ -405,7 +405,7 @@ extern "C" int qv_linear_scan(int kind, float* out, int ld_out, const void* q, i
 //   gate_first = 1:  u = y * silu(gate);  out = u / rms_part(u) * w
 // One block per (token, part).
 template <typename T>
-__global__ void __launch_bounds__(128) gated_group_norm_kernel(T* __restrict__ out, int ld_out, const float* __restrict__ y, int ld_y,
+__global__ void __launch_bounds__(1024) gated_group_norm_kernel(T* __restrict__ out, int ld_out, const float* __restrict__ y, int ld_y,
                                                                const T* __restrict__ gate, int ld_gate, const float* __restrict__ w,
                                                                int part, float eps, int gate_first) {
   __shared__ float red[33];
@@ -437,8 +437,11 @@ extern "C" int qv_gated_group_norm(void* out, int ld_out, const float* y, int ld
                                    int T, int width, int groups, float eps, int gate_first, int dt, void* stream) {
   if (T <= 0) return 0;
   if (groups <= 0 || width % groups || groups > 65535) return QV_ERR_UNSUPPORTED;
+  // one element a thread up to 1024; the block's size, and so the order of the sums, follows from the part's width alone
+  const int part_w = width / groups;
+  const int threads = part_w >= 1024 ? 1024 : (part_w <= 128 ? 128 : ((part_w + 31) / 32) * 32);
   QV_DISPATCH_DT(dt, TT,
-                 return qv_launch(gated_group_norm_kernel<TT>, dim3(T, groups), dim3(128), 0, (cudaStream_t)stream, (TT*)out, ld_out, y,
+                 return qv_launch(gated_group_norm_kernel<TT>, dim3(T, groups), dim3(threads), 0, (cudaStream_t)stream, (TT*)out, ld_out, y,
                                   ld_y, (const TT*)gate, ld_gate, w, width / groups, eps, gate_first));
   return QV_ERR_UNSUPPORTED;
 }

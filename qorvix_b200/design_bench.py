@@ -170,9 +170,9 @@ def experts_case(T, peaks) -> dict:
     E, top, ff, d = MOE["router"]["experts"], MOE["router"]["top"], MOE["expert"]["ff"], WIDTH
     wbytes = E * 3 * ff * d * 2
     copies = max(2, int(2.5 * kb.L2_BYTES // wbytes) + 1)
-    wg = [torch.randn(E, ff, d, device="cuda", dtype=torch.bfloat16) * 0.02 for _ in range(copies)]
-    wu = [torch.randn(E, ff, d, device="cuda", dtype=torch.bfloat16) * 0.02 for _ in range(copies)]
-    wd = [torch.randn(E, d, ff, device="cuda", dtype=torch.bfloat16) * 0.02 for _ in range(copies)]
+    wg = [ops.moe_pack_experts(torch.randn(E, ff, d, device="cuda", dtype=torch.bfloat16) * 0.02) for _ in range(copies)]
+    wu = [ops.moe_pack_experts(torch.randn(E, ff, d, device="cuda", dtype=torch.bfloat16) * 0.02) for _ in range(copies)]
+    wd = [ops.moe_pack_experts(torch.randn(E, d, ff, device="cuda", dtype=torch.bfloat16) * 0.02) for _ in range(copies)]
     router = torch.randn(E, d, device="cuda", dtype=torch.bfloat16)
     x = torch.randn(T, d, device="cuda", dtype=torch.bfloat16)
     R = T * top
@@ -188,8 +188,8 @@ def experts_case(T, peaks) -> dict:
     def run(i):
         ops.moe_route(top_idx, top_w, None, x, router, None)
         ops.moe_group(row_token, slot_row, tiles, top_idx, scratch, E, tile_rows)
-        ops.moe_experts(True, act, x, wg[i % copies], wu[i % copies], row_token, tiles, True)
-        ops.moe_experts(False, y, act, wd[i % copies], None, row_token, tiles, True)
+        ops.moe_experts_tc(True, act, x, wg[i % copies], wu[i % copies], row_token, tiles)
+        ops.moe_experts_tc(False, y, act, wd[i % copies], None, row_token, tiles)
         ops.moe_combine(delta, None, y, slot_row, top_w, None, None)
 
     us = kb.timed_chain(run, launches=6)

@@ -21,6 +21,12 @@ class RoutedFeedForward(FeedForward):
         self.w_gate = torch.stack([source.get(g) for g, _, _ in names]).contiguous()      # [E, ff, d]
         self.w_up = torch.stack([source.get(u) for _, u, _ in names]).to(self.w_gate.dtype).contiguous()
         self.w_down = torch.stack([source.get(dn) for _, _, dn in names]).to(self.w_gate.dtype).contiguous()   # [E, d, ff]
+        # bfloat16 with rows that start on 16 bytes: the tensor-core kernel, over matrices packed in 64 x 64 tiles
+        # (the rows are then dropped)
+        self.tensor_cores = (rt.dtype == torch.bfloat16 and self.w_gate.dtype == torch.bfloat16 and spec.hidden_size % 8 == 0
+                             and spec.expert_ff % 8 == 0)
+        if self.tensor_cores:
+            self.w_gate, self.w_up, self.w_down = (ops.moe_pack_experts(w) for w in (self.w_gate, self.w_up, self.w_down))
         self.shared = build_part("feed_forward", spec.shared, source, rt)
         self.shared_gate = source.get(spec.shared_gate).to(self.router.dtype).reshape(-1) if spec.shared is not None else None
 
@@ -33,15 +39,19 @@ class RoutedFeedForward(FeedForward):
         top_w = torch.empty((T, s.top), device=dev, dtype=torch.float32)
         gate = torch.empty(T, device=dev, dtype=torch.float32) if self.shared is not None else None
         ops.moe_route(top_idx, top_w, gate, x, self.router, self.shared_gate)
-        tc = ops.moe_tensor_cores(x, self.w_up, self.w_down)
+        tc = self.tensor_cores
         tile_rows = ops.moe_tile_rows(tc)
         ints = torch.empty(3 * R + 3 * ops.moe_max_tiles(R, s.experts, tile_rows), device=dev, dtype=torch.int32)
         row_token, slot_row, scratch, tiles = ints[:R], ints[R: 2 * R], ints[2 * R: 3 * R], ints[3 * R:]
         ops.moe_group(row_token, slot_row, tiles, top_idx, scratch, s.experts, tile_rows)
         act = torch.empty((R, s.expert_ff), device=dev, dtype=x.dtype)
-        ops.moe_experts(True, act, x, self.w_gate, self.w_up, row_token, tiles, tc)
         y = torch.empty((R, d), device=dev, dtype=torch.float32)
-        ops.moe_experts(False, y, act, self.w_down, None, row_token, tiles, tc)
+        if tc:
+            ops.moe_experts_tc(True, act, x, self.w_gate, self.w_up, row_token, tiles)
+            ops.moe_experts_tc(False, y, act, self.w_down, None, row_token, tiles)
+        else:
+            ops.moe_experts(True, act, x, self.w_gate, self.w_up, row_token, tiles)
+            ops.moe_experts(False, y, act, self.w_down, None, row_token, tiles)
         shared = self.shared.forward(x, ctx) if self.shared is not None else None
         delta = torch.empty((T, d), device=dev, dtype=torch.float32)
         ops.moe_combine(delta, add, y, slot_row, top_w, shared, gate)
