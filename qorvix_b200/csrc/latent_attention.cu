@@ -354,19 +354,20 @@ __global__ void __launch_bounds__(LT_WARPS * 32) latent_attention_tc_kernel(
   const int* bt = block_table + (size_t)s * max_blocks;
   const int pieces = kw / 8;                               // 16-byte pieces of a row
 
+  // a warp copies whole rows (one page lookup a row, the row's 16-byte pieces dealt to the lanes)
   auto load_keys = [&](int buf, int blk) {
     bf16* dst = Ks + (size_t)buf * LT_BK * ldk;
-    for (int c = tid; c < LT_BK * pieces; c += LT_WARPS * 32) {
-      const int r = c / pieces, p = c - r * pieces, key = blk * LT_BK + r;
+    for (int r = warp; r < LT_BK; r += LT_WARPS) {
+      const int key = blk * LT_BK + r;
       const bool ok = key <= pos_last;
-      const bf16* src = cache + (ok ? ((size_t)bt[key / page] * page + (size_t)(key % page)) * kw + p * 8 : 0);
-      lt_cp16(dst + (size_t)r * ldk + p * 8, src, ok ? 16 : 0);
+      const bf16* src = cache + (ok ? ((size_t)bt[key / page] * page + (size_t)(key % page)) * kw : 0);
+      for (int p = lane; p < pieces; p += 32) lt_cp16(dst + (size_t)r * ldk + p * 8, src + (ok ? p * 8 : 0), ok ? 16 : 0);
     }
   };
-  for (int c = tid; c < LT_BM * pieces; c += LT_WARPS * 32) {
-    const int r = c / pieces, p = c - r * pieces;
+  for (int r = warp; r < LT_BM; r += LT_WARPS) {
     const bool ok = r < rows;
-    lt_cp16(Qs + (size_t)r * ldk + p * 8, qlat + (ok ? (size_t)(row_first + r) * kw + p * 8 : 0), ok ? 16 : 0);
+    const bf16* src = qlat + (ok ? (size_t)(row_first + r) * kw : 0);
+    for (int p = lane; p < pieces; p += 32) lt_cp16(Qs + (size_t)r * ldk + p * 8, src + (ok ? p * 8 : 0), ok ? 16 : 0);
   }
   if (b_lo < b_hi) load_keys(0, b_lo);
   asm volatile("cp.async.commit_group;" ::: "memory");
@@ -404,15 +405,28 @@ __global__ void __launch_bounds__(LT_WARPS * 32) latent_attention_tc_kernel(
     __syncthreads();
     const bf16* Kb = Ks + (size_t)buf * LT_BK * ldk;
     // scores of this warp's eight keys for all 32 rows
-    float sc[2][4] = {};
-    for (int ks = 0; ks < kw / 16; ++ks) {
+    float sc[2][4] = {}, sd[2][4] = {};                      // two chains of dependent products instead of one
+    const int nks = kw / 16;
+    for (int ks = 0; ks < nks; ks += 2) {
       uint32_t a[2][4], b[2];
       lt_ldsm4(a[0], Qs + (size_t)(lane & 15) * ldk + ks * 16 + (lane >> 4) * 8);
       lt_ldsm4(a[1], Qs + (size_t)(16 + (lane & 15)) * ldk + ks * 16 + (lane >> 4) * 8);
       lt_ldsm2(b, Kb + (size_t)(warp * 8 + (lane & 7)) * ldk + ks * 16 + ((lane >> 3) & 1) * 8);
       lt_mma(sc[0], a[0], b);
       lt_mma(sc[1], a[1], b);
+      if (ks + 1 < nks) {
+        uint32_t c[2][4], e[2];
+        lt_ldsm4(c[0], Qs + (size_t)(lane & 15) * ldk + (ks + 1) * 16 + (lane >> 4) * 8);
+        lt_ldsm4(c[1], Qs + (size_t)(16 + (lane & 15)) * ldk + (ks + 1) * 16 + (lane >> 4) * 8);
+        lt_ldsm2(e, Kb + (size_t)(warp * 8 + (lane & 7)) * ldk + (ks + 1) * 16 + ((lane >> 3) & 1) * 8);
+        lt_mma(sd[0], c[0], e);
+        lt_mma(sd[1], c[1], e);
+      }
     }
+#pragma unroll
+    for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+      for (int x = 0; x < 4; ++x) sc[mt][x] += sd[mt][x];
     const int key0 = blk * LT_BK + warp * 8 + 2 * (lane & 3);
 #pragma unroll
     for (int mt = 0; mt < 2; ++mt)
