@@ -193,18 +193,20 @@ __global__ void __launch_bounds__(SCAN_VT * SCAN_WARPS) linear_scan_kernel(ScanA
 // summation order are those of linear_scan_kernel; the state's layout in memory is the same.
 #define SCAN_TB 4
 #define SCAN_CH 256      // tokens whose gates are worked out together (one a thread)
-template <typename T, int KIND, int RPT>
+// ASYNC: the rows of q and k start on 16 bytes, and the next four tokens' rows are copied into the other of two
+// buffers by cp.async while the present four are worked on (else plain loads ahead of the work).
+template <typename T, int KIND, int RPT, bool ASYNC>
 __global__ void __launch_bounds__(SCAN_VT * SCAN_WARPS) linear_scan_reg_kernel(ScanArgs a) {
-  extern __shared__ float sm[];
+  extern __shared__ __align__(16) float sm[];
   pdl_wait();
   pdl_launch_dependents();
   const int s = blockIdx.x, h = blockIdx.y, tile = blockIdx.z;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int dk = a.dk, dv = a.dv;
   const int tiles = (dv + SCAN_VT - 1) / SCAN_VT;
-  float* qs = sm;                                  // [TB][dk]
-  float* ks = qs + SCAN_TB * dk;                   // [TB][dk]
-  float* ns = ks + SCAN_TB * dk;                   // [dk]
+  const int rowpad = (dk + 7) & ~7;                // a token's row in the buffers (elements): whole 16-byte pieces
+  T* raw = (T*)sm;                                 // [2 buffers][q, k][TB][rowpad] as stored (the scale of q is applied to the sums)
+  float* ns = sm + (4 * SCAN_TB * rowpad * sizeof(T) + 3) / 4;   // [dk]
   float* red = ns + dk;                            // [TB][SCAN_WARPS][32]
   float* sc = red + SCAN_TB * SCAN_WARPS * SCAN_VT;  // [TB]
   float* gk = sc + SCAN_TB;                        // [SCAN_CH] keep factors of the tokens in work
@@ -231,6 +233,19 @@ __global__ void __launch_bounds__(SCAN_VT * SCAN_WARPS) linear_scan_reg_kernel(S
   const T* vb = (const T*)a.v + (size_t)h * dv;
   const float b1 = a.p1 ? a.p1[h] : 0.f, b2 = a.p2 ? a.p2[h] : 0.f, b3 = a.p3 ? a.p3[h] : 0.f;
   const float rate = KIND == SCAN_DECAY ? expf(b2) : 0.f;
+  auto issue = [&](int buf, int j0) {
+    const int nb = len - j0 < SCAN_TB ? len - j0 : SCAN_TB;
+    const int pieces = dk * (int)sizeof(T) / 16, per = 16 / (int)sizeof(T);
+    T* dst = raw + (size_t)buf * 2 * SCAN_TB * rowpad;
+    for (int c = threadIdx.x; c < 2 * nb * pieces; c += blockDim.x) {
+      const int which = c / (nb * pieces), rem = c - which * nb * pieces, tt = rem / pieces, pc = rem - tt * pieces;
+      const T* src = (which ? kb + (size_t)(q0 + j0 + tt) * a.ld_k : qb + (size_t)(q0 + j0 + tt) * a.ld_q) + pc * per;
+      const unsigned sa = (unsigned)__cvta_generic_to_shared(dst + (which * SCAN_TB + tt) * rowpad + pc * per);
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(sa), "l"(src) : "memory");
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+  if (ASYNC) issue(0, 0);
   // Gates are worked out for 256 tokens at a time, one token a thread, and kept in shared memory: the transcendental
   // functions then lie off the path from one token to the next.  Only the running maximum is a chain (thread 0).
   for (int c0 = 0; c0 < len; c0 += SCAN_CH) {
@@ -274,10 +289,18 @@ __global__ void __launch_bounds__(SCAN_VT * SCAN_WARPS) linear_scan_reg_kernel(S
   for (int j0 = c0; j0 < c0 + nch; j0 += SCAN_TB) {
     const int nb = c0 + nch - j0 < SCAN_TB ? c0 + nch - j0 : SCAN_TB;
     const size_t t0 = (size_t)(q0 + j0);
-    for (int c = threadIdx.x; c < nb * dk; c += blockDim.x) {
-      const int tt = c / dk, i = c - tt * dk;
-      qs[c] = to_f(qb[(t0 + tt) * a.ld_q + i]) * a.q_scale;
-      ks[c] = to_f(kb[(t0 + tt) * a.ld_k + i]);
+    const int buf = (j0 / SCAN_TB) & 1;
+    const T* qs = raw + (size_t)buf * 2 * SCAN_TB * rowpad;
+    const T* ks = qs + SCAN_TB * rowpad;
+    if (ASYNC) {
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
+    } else {
+      T* wq = raw + (size_t)buf * 2 * SCAN_TB * rowpad;
+      for (int c = threadIdx.x; c < nb * dk; c += blockDim.x) {
+        const int tt = c / dk, i = c - tt * dk;
+        wq[tt * rowpad + i] = qb[(t0 + tt) * a.ld_q + i];
+        wq[(SCAN_TB + tt) * rowpad + i] = kb[(t0 + tt) * a.ld_k + i];
+      }
     }
     float vv[SCAN_TB], keep[SCAN_TB], take[SCAN_TB], mt[SCAN_TB];
 #pragma unroll
@@ -291,16 +314,17 @@ __global__ void __launch_bounds__(SCAN_VT * SCAN_WARPS) linear_scan_reg_kernel(S
       }
     }
     __syncthreads();                       // the four tokens' q and k are in place; red and sc of the last four have been read
+    if (ASYNC && j0 + SCAN_TB < len) issue(buf ^ 1, j0 + SCAN_TB);
     if (KIND == SCAN_GATED_MAX && warp == 0) {
       for (int tt = 0; tt < nb; ++tt) {
         float dot = 0.f;
         for (int i = lane; i < dk; i += 32) {
-          const float n = keep[tt] * ns[i] + take[tt] * ks[tt * dk + i];
+          const float n = keep[tt] * ns[i] + take[tt] * to_f(ks[tt * rowpad + i]);
           ns[i] = n;
-          dot = fmaf(n, qs[tt * dk + i], dot);
+          dot = fmaf(n, to_f(qs[tt * rowpad + i]), dot);
         }
         dot = warp_sum(dot);
-        if (lane == 0) sc[tt] = dot;
+        if (lane == 0) sc[tt] = dot * a.q_scale;
       }
     }
 #pragma unroll
@@ -312,8 +336,8 @@ __global__ void __launch_bounds__(SCAN_VT * SCAN_WARPS) linear_scan_reg_kernel(S
         for (int i = 0; i < RPT; ++i) {
           const int k = warp + SCAN_WARPS * i;
           if (k < dk) {
-            S[i] = fmaf(keep[tt], S[i], tv * ks[tt * dk + k]);
-            acc = fmaf(S[i], qs[tt * dk + k], acc);
+            S[i] = fmaf(keep[tt], S[i], tv * to_f(ks[tt * rowpad + k]));
+            acc = fmaf(S[i], to_f(qs[tt * rowpad + k]), acc);
           }
         }
         red[(tt * SCAN_WARPS + warp) * SCAN_VT + lane] = acc;
@@ -325,6 +349,7 @@ __global__ void __launch_bounds__(SCAN_VT * SCAN_WARPS) linear_scan_reg_kernel(S
       float y = 0.f;
 #pragma unroll
       for (int w = 0; w < SCAN_WARPS; ++w) y += red[(tt * SCAN_WARPS + w) * SCAN_VT + lane];
+      y *= a.q_scale;
       // vv and mt of token tt, which this thread holds at a compile-time index only: pick without indexing registers
       float v_tt = vv[0], m_tt = mt[0];
 #pragma unroll
@@ -368,9 +393,17 @@ extern "C" int qv_linear_scan(int kind, float* out, int ld_out, const void* q, i
   dim3 grid(S, H, tiles);
   cudaStream_t st = (cudaStream_t)stream;
   if (dk <= 8 * 32) {                      // the state fits the registers
-    const size_t smem_r = ((size_t)(2 * SCAN_TB + 1) * dk + SCAN_TB * SCAN_WARPS * SCAN_VT + SCAN_TB + 4 * SCAN_CH) * sizeof(float);
+    const size_t esz = dt == QV_DT_F32 ? 4 : 2;
+    const size_t rowpad = (size_t)((dk + 7) & ~7);
+    const size_t smem_r = ((4 * SCAN_TB * rowpad * esz + 3) / 4 + dk + SCAN_TB * SCAN_WARPS * SCAN_VT + SCAN_TB + 4 * SCAN_CH) * sizeof(float);
+    const bool async = (dk * esz) % 16 == 0 && ((size_t)ld_q * esz) % 16 == 0 && ((size_t)ld_k * esz) % 16 == 0 &&
+                       (((uintptr_t)q | (uintptr_t)k) & 15) == 0;
     const int rpt = dk <= 32 ? 4 : dk <= 64 ? 8 : dk <= 128 ? 16 : 32;
-#define LAUNCH_REG(TT, KIND, RPT) return qv_launch(linear_scan_reg_kernel<TT, KIND, RPT>, grid, dim3(SCAN_VT * SCAN_WARPS), smem_r, st, a)
+#define LAUNCH_REG(TT, KIND, RPT)                                                                                             \
+  do {                                                                                                                        \
+    if (async) return qv_launch(linear_scan_reg_kernel<TT, KIND, RPT, true>, grid, dim3(SCAN_VT * SCAN_WARPS), smem_r, st, a); \
+    return qv_launch(linear_scan_reg_kernel<TT, KIND, RPT, false>, grid, dim3(SCAN_VT * SCAN_WARPS), smem_r, st, a);          \
+  } while (0)
 #define LAUNCH_REG_RPT(TT, KIND)                  \
   do {                                            \
     if (rpt == 4) LAUNCH_REG(TT, KIND, 4);        \
