@@ -96,7 +96,10 @@ struct ScanArgs {
   int H, dk, dv;
 };
 
-__host__ __device__ inline int scan_tile_floats(int kind, int dk) { return dk * SCAN_VT + (kind == SCAN_GATED_MAX ? dk + 1 : 0); }
+__host__ __device__ inline int scan_tile_floats(int kind, int dk, int vt = SCAN_VT) { return dk * vt + (kind == SCAN_GATED_MAX ? dk + 1 : 0); }
+// Value columns a CTA owns: 32, or 16 for key sizes of 129..256, where a thread would else keep 32 rows (more than
+// its registers hold) and wide heads give few CTAs.  A function of the key size alone: the state's layout follows it.
+static inline int scan_vt(int dk) { return (dk > 128 && dk <= 256) ? 16 : 32; }
 
 template <typename T, int KIND>
 __global__ void __launch_bounds__(SCAN_VT * SCAN_WARPS) linear_scan_kernel(ScanArgs a) {
@@ -195,7 +198,7 @@ __global__ void __launch_bounds__(SCAN_VT * SCAN_WARPS) linear_scan_kernel(ScanA
 #define SCAN_CH 256      // tokens whose gates are worked out together (one a thread)
 // ASYNC: the rows of q and k start on 16 bytes, and the next four tokens' rows are copied into the other of two
 // buffers by cp.async while the present four are worked on (else plain loads ahead of the work).
-template <typename T, int KIND, int RPT, bool ASYNC>
+template <typename T, int KIND, int RPT, bool ASYNC, int VT>
 __global__ void __launch_bounds__(SCAN_VT * SCAN_WARPS) linear_scan_reg_kernel(ScanArgs a) {
   extern __shared__ __align__(16) float sm[];
   pdl_wait();
@@ -203,7 +206,9 @@ __global__ void __launch_bounds__(SCAN_VT * SCAN_WARPS) linear_scan_reg_kernel(S
   const int s = blockIdx.x, h = blockIdx.y, tile = blockIdx.z;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int dk = a.dk, dv = a.dv;
-  const int tiles = (dv + SCAN_VT - 1) / SCAN_VT;
+  constexpr int RS = 32 / VT;                       // row groups a warp: with 16 columns a tile, the lanes' halves take alternate rows
+  const int cl = lane % VT, rsub = lane / VT;
+  const int tiles = (dv + VT - 1) / VT;
   const int rowpad = (dk + 7) & ~7;                // a token's row in the buffers (elements): whole 16-byte pieces
   T* raw = (T*)sm;                                 // [2 buffers][q, k][TB][rowpad] as stored (the scale of q is applied to the sums)
   float* ns = sm + (4 * SCAN_TB * rowpad * sizeof(T) + 3) / 4;   // [dk]
@@ -214,19 +219,19 @@ __global__ void __launch_bounds__(SCAN_VT * SCAN_WARPS) linear_scan_reg_kernel(S
   float* ge = gt + SCAN_CH;                        // [SCAN_CH] exp(-m) (GATED_MAX)
   float* gm = ge + SCAN_CH;                        // [SCAN_CH] scratch of the running maximum
   const int q0 = a.seg_q_start[s], len = a.seg_q_start[s + 1] - q0;
-  float* st = a.state + (size_t)a.seg_slot[s] * a.slot_stride + ((size_t)h * tiles + tile) * scan_tile_floats(KIND, dk);
+  float* st = a.state + (size_t)a.seg_slot[s] * a.slot_stride + ((size_t)h * tiles + tile) * scan_tile_floats(KIND, dk, VT);
   float S[RPT];
 #pragma unroll
   for (int i = 0; i < RPT; ++i) {
-    const int k = warp + SCAN_WARPS * i;
-    S[i] = k < dk ? st[k * SCAN_VT + lane] : 0.f;
+    const int k = warp * RS + rsub + SCAN_WARPS * RS * i;
+    S[i] = k < dk ? st[k * VT + cl] : 0.f;
   }
   float m = 0.f;
   if (KIND == SCAN_GATED_MAX) {
-    for (int i = threadIdx.x; i < dk; i += blockDim.x) ns[i] = st[dk * SCAN_VT + i];
-    m = st[dk * SCAN_VT + dk];
+    for (int i = threadIdx.x; i < dk; i += blockDim.x) ns[i] = st[dk * VT + i];
+    m = st[dk * VT + dk];
   }
-  const int col = tile * SCAN_VT + lane;
+  const int col = tile * VT + cl;
   const bool live = col < dv;
   const T* qb = (const T*)a.q + (size_t)(h / a.q_group) * dk;
   const T* kb = (const T*)a.k + (size_t)(h / a.q_group) * dk;
@@ -334,7 +339,7 @@ __global__ void __launch_bounds__(SCAN_VT * SCAN_WARPS) linear_scan_reg_kernel(S
         const float tv = take[tt] * vv[tt];
 #pragma unroll
         for (int i = 0; i < RPT; ++i) {
-          const int k = warp + SCAN_WARPS * i;
+          const int k = warp * RS + rsub + SCAN_WARPS * RS * i;
           if (k < dk) {
             S[i] = fmaf(keep[tt], S[i], tv * to_f(ks[tt * rowpad + k]));
             acc = fmaf(S[i], to_f(qs[tt * rowpad + k]), acc);
@@ -344,11 +349,13 @@ __global__ void __launch_bounds__(SCAN_VT * SCAN_WARPS) linear_scan_reg_kernel(S
       }
     }
     __syncthreads();
-    if (warp < nb && live) {
+    if (warp < nb && live && rsub == 0) {
       const int tt = warp;
       float y = 0.f;
 #pragma unroll
-      for (int w = 0; w < SCAN_WARPS; ++w) y += red[(tt * SCAN_WARPS + w) * SCAN_VT + lane];
+      for (int w = 0; w < SCAN_WARPS; ++w)
+#pragma unroll
+        for (int g = 0; g < RS; ++g) y += red[(tt * SCAN_WARPS + w) * SCAN_VT + g * VT + cl];
       y *= a.q_scale;
       // vv and mt of token tt, which this thread holds at a compile-time index only: pick without indexing registers
       float v_tt = vv[0], m_tt = mt[0];
@@ -363,17 +370,18 @@ __global__ void __launch_bounds__(SCAN_VT * SCAN_WARPS) linear_scan_reg_kernel(S
   __syncthreads();
 #pragma unroll
   for (int i = 0; i < RPT; ++i) {
-    const int k = warp + SCAN_WARPS * i;
-    if (k < dk) st[k * SCAN_VT + lane] = S[i];
+    const int k = warp * RS + rsub + SCAN_WARPS * RS * i;
+    if (k < dk) st[k * VT + cl] = S[i];
   }
   if (KIND == SCAN_GATED_MAX) {
-    for (int i = threadIdx.x; i < dk; i += blockDim.x) st[dk * SCAN_VT + i] = ns[i];
-    if (threadIdx.x == 0) st[dk * SCAN_VT + dk] = m;
+    for (int i = threadIdx.x; i < dk; i += blockDim.x) st[dk * VT + i] = ns[i];
+    if (threadIdx.x == 0) st[dk * VT + dk] = m;
   }
 }
 
 extern "C" long long qv_linear_scan_state_floats(int kind, int H, int dk, int dv) {
-  return (long long)H * ((dv + SCAN_VT - 1) / SCAN_VT) * scan_tile_floats(kind, dk);
+  const int vt = scan_vt(dk);
+  return (long long)H * ((dv + vt - 1) / vt) * scan_tile_floats(kind, dk, vt);
 }
 
 extern "C" int qv_linear_scan(int kind, float* out, int ld_out, const void* q, int ld_q, int q_group, const void* k, int ld_k,
@@ -383,7 +391,8 @@ extern "C" int qv_linear_scan(int kind, float* out, int ld_out, const void* q, i
   if (S <= 0) return 0;
   if (kind != SCAN_GATED_MAX && kind != SCAN_DECAY) return QV_ERR_UNSUPPORTED;
   if (H <= 0 || dk <= 0 || dv <= 0 || q_group <= 0 || H > 65535) return QV_ERR_UNSUPPORTED;
-  const int tiles = (dv + SCAN_VT - 1) / SCAN_VT;
+  const int vt = scan_vt(dk);
+  const int tiles = (dv + vt - 1) / vt;
   const size_t smem = ((size_t)dk * SCAN_VT + 3 * (size_t)dk + SCAN_WARPS * SCAN_VT + 2) * sizeof(float);
   if (smem > 200 * 1024 || tiles > 65535) return QV_ERR_TOO_LARGE;
   ScanArgs a;
@@ -398,18 +407,21 @@ extern "C" int qv_linear_scan(int kind, float* out, int ld_out, const void* q, i
     const size_t smem_r = ((4 * SCAN_TB * rowpad * esz + 3) / 4 + dk + SCAN_TB * SCAN_WARPS * SCAN_VT + SCAN_TB + 4 * SCAN_CH) * sizeof(float);
     const bool async = (dk * esz) % 16 == 0 && ((size_t)ld_q * esz) % 16 == 0 && ((size_t)ld_k * esz) % 16 == 0 &&
                        (((uintptr_t)q | (uintptr_t)k) & 15) == 0;
-    const int rpt = dk <= 32 ? 4 : dk <= 64 ? 8 : dk <= 128 ? 16 : 32;
+    const int rpt = dk <= 32 ? 4 : dk <= 64 ? 8 : 16;          // 129..256 rows: 16 columns a tile, two row groups a warp
 #define LAUNCH_REG(TT, KIND, RPT)                                                                                             \
   do {                                                                                                                        \
-    if (async) return qv_launch(linear_scan_reg_kernel<TT, KIND, RPT, true>, grid, dim3(SCAN_VT * SCAN_WARPS), smem_r, st, a); \
-    return qv_launch(linear_scan_reg_kernel<TT, KIND, RPT, false>, grid, dim3(SCAN_VT * SCAN_WARPS), smem_r, st, a);          \
+    if (vt == 16) {                                                                                                           \
+      if (async) return qv_launch(linear_scan_reg_kernel<TT, KIND, 16, true, 16>, grid, dim3(SCAN_VT * SCAN_WARPS), smem_r, st, a); \
+      return qv_launch(linear_scan_reg_kernel<TT, KIND, 16, false, 16>, grid, dim3(SCAN_VT * SCAN_WARPS), smem_r, st, a);     \
+    }                                                                                                                         \
+    if (async) return qv_launch(linear_scan_reg_kernel<TT, KIND, RPT, true, 32>, grid, dim3(SCAN_VT * SCAN_WARPS), smem_r, st, a); \
+    return qv_launch(linear_scan_reg_kernel<TT, KIND, RPT, false, 32>, grid, dim3(SCAN_VT * SCAN_WARPS), smem_r, st, a);      \
   } while (0)
 #define LAUNCH_REG_RPT(TT, KIND)                  \
   do {                                            \
     if (rpt == 4) LAUNCH_REG(TT, KIND, 4);        \
     if (rpt == 8) LAUNCH_REG(TT, KIND, 8);        \
-    if (rpt == 16) LAUNCH_REG(TT, KIND, 16);      \
-    LAUNCH_REG(TT, KIND, 32);                     \
+    LAUNCH_REG(TT, KIND, 16);                     \
   } while (0)
     if (dt == QV_DT_F32 && kind == SCAN_GATED_MAX) LAUNCH_REG_RPT(float, SCAN_GATED_MAX);
     if (dt == QV_DT_F32 && kind == SCAN_DECAY) LAUNCH_REG_RPT(float, SCAN_DECAY);

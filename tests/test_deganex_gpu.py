@@ -93,7 +93,9 @@ MIXER_CASES = [dh.attn(), dh.attn(heads=1, dim=8, rot_dim=16, vdim=36, kv_rank=2
                dh.attn(heads=16, dim=8, rot_dim=16, vdim=8, kv_rank=64),           # sizes the tensor-core kernels take
                dh.mlstm(), dh.mlstm(heads=1, dim=33, vdim=16, gate_cap=3.0), dh.mlstm(heads=2, dim=7, vdim=70, gate_cap=15.0),
                dh.mamba(), dh.mamba(heads=2, vdim=40, state=12, groups=2, conv=2, norm_groups=1),
-               dh.mamba(heads=4, vdim=16, state=36, groups=1, conv=5, norm_groups=2)]
+               dh.mamba(heads=4, vdim=16, state=36, groups=1, conv=5, norm_groups=2),
+               dh.mlstm(heads=2, dim=136, vdim=24, gate_cap=6.0), dh.mamba(heads=2, vdim=40, state=160, groups=1, conv=4, norm_groups=1),   # key sizes of 129..256: 16-column tiles
+               dh.mlstm(heads=1, dim=264, vdim=8, gate_cap=6.0)]                                     # beyond 256: the state stays in shared memory
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
