@@ -334,6 +334,7 @@ __global__ void embed_pair_kernel(float* __restrict__ out, const TW* __restrict_
     int prev = t > first ? ids[t - 1] : last_token[seg_slot[s]];
     if (prev < 0 || prev >= vocab) prev = 0;
     row = ((long long)prev * mul_prev + (long long)id * mul_cur) % buckets;
+    if (row < 0) row += buckets;            // the mathematical remainder, also for negative multipliers
   }
   __syncthreads();                          // every thread has read the kept token before it is replaced
   if (t == first && threadIdx.x == 0) last_token[seg_slot[s]] = ids[seg_q_start[s + 1] - 1];

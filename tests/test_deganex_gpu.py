@@ -201,10 +201,11 @@ def test_bigram_embedding_alone(dtype):
     vocab, width, buckets = 50, 24, 11
     emb, pair = rnd(vocab, width, seed=1).to(torch.bfloat16), rnd(buckets + 1, width, seed=2).to(torch.bfloat16)
     src = TensorSource(tensors={"e": emb, "p": pair}, device=DEV, compute_dtype=dtype)
-    part = build_part("embedding", BigramEmbeddingSpec(vocab, width, "e", "p", buckets, 5, 3), src, Runtime(DEV, dtype, 64))
+    mul_prev, mul_cur = (5, 3) if dtype == torch.float32 else (-7, 100003)       # also a negative and a large multiplier
+    part = build_part("embedding", BigramEmbeddingSpec(vocab, width, "e", "p", buckets, mul_prev, mul_cur), src, Runtime(DEV, dtype, 64))
     cache = CacheManager([(part.cache_spec(), None)], max_tokens=64, page_size=16, max_requests=2, device=DEV, dtype=dtype)
     toks = [int(t) for t in torch.randint(0, vocab, (40,), generator=torch.Generator().manual_seed(3))]
-    want = plain.embed_bigram(toks, emb.double(), pair.double(), buckets, 5, 3)
+    want = plain.embed_bigram(toks, emb.double(), pair.double(), buckets, mul_prev, mul_cur)
     builder = BatchBuilder(DEV)
     for rid in ("a", "b", "c"):                                  # 'c' takes the slot 'a' gave back: its first token is a first token
         cache.admit(rid)
