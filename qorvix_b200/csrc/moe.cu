@@ -15,21 +15,10 @@
 #include "common.cuh"
 
 #define ROUTE_WARPS 8
-template <typename T, typename TW>
-__global__ void __launch_bounds__(ROUTE_WARPS * 32) moe_route_kernel(int* __restrict__ top_idx, float* __restrict__ top_w, float* __restrict__ gate_out,
-                                                        const T* __restrict__ h, int ld_h, const TW* __restrict__ wr,
-                                                        const TW* __restrict__ wg, int d, int E, int top) {
-  extern __shared__ float logit[];           // E floats, then the token's d inputs
-  pdl_wait();
-  pdl_launch_dependents();
-  const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  float* xs = logit + E;
-  const T* x = h + (size_t)t * ld_h;
-  for (int i = threadIdx.x; i < d; i += blockDim.x) xs[i] = to_f(x[i]);
-  __syncthreads();
-  for (int e = warp; e < E + (wg ? 1 : 0); e += ROUTE_WARPS) {
-    const TW* w = e < E ? wr + (size_t)e * d : wg;
-    // 16-byte loads, eight in flight per lane, where the rows allow; the order of the sum depends on d only
+// One warp's dot product of a weight row with the token's inputs (float32 in shared memory), summed over the warp.
+template <typename TW>
+__device__ __forceinline__ float route_dot(const TW* __restrict__ w, const float* __restrict__ xs, int d, int lane) {
+  // 16-byte loads, eight in flight per lane, where the rows allow; the order of the sum depends on d only
     float acc = 0.f;
     constexpr int VEC = 16 / (int)sizeof(TW);
     int i = 0;
@@ -61,7 +50,47 @@ __global__ void __launch_bounds__(ROUTE_WARPS * 32) moe_route_kernel(int* __rest
       }
       for (; i < d; i += 32) acc = fmaf(to_f(w[i]), xs[i], acc);
     }
-    acc = warp_sum(acc);
+    return warp_sum(acc);
+}
+
+// logits[t][e] = wr[e] . h[t] for e < E, and logits[t][E] = wg . h[t] when wg is given: eight rows a CTA, so that a
+// step of few tokens still spreads the router's matrix over many SMs.
+template <typename T, typename TW>
+__global__ void __launch_bounds__(ROUTE_WARPS * 32) moe_logits_kernel(float* __restrict__ logits, const T* __restrict__ h, int ld_h,
+                                                                      const TW* __restrict__ wr, const TW* __restrict__ wg, int d, int E) {
+  extern __shared__ float xs_only[];
+  pdl_wait();
+  pdl_launch_dependents();
+  const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const T* x = h + (size_t)t * ld_h;
+  for (int i = threadIdx.x; i < d; i += blockDim.x) xs_only[i] = to_f(x[i]);
+  __syncthreads();
+  const int e = blockIdx.y * ROUTE_WARPS + warp;
+  if (e >= E + (wg ? 1 : 0)) return;
+  const float acc = route_dot(e < E ? wr + (size_t)e * d : wg, xs_only, d, lane);
+  if (lane == 0) logits[(size_t)t * (E + 1) + e] = acc;
+}
+
+// pre: logits worked out by moe_logits_kernel ([T][E + 1]), or null: then this kernel forms them itself.
+template <typename T, typename TW>
+__global__ void __launch_bounds__(ROUTE_WARPS * 32) moe_route_kernel(int* __restrict__ top_idx, float* __restrict__ top_w, float* __restrict__ gate_out,
+                                                        const T* __restrict__ h, int ld_h, const TW* __restrict__ wr,
+                                                        const TW* __restrict__ wg, int d, int E, int top, const float* __restrict__ pre) {
+  extern __shared__ float logit[];           // E floats, then the token's d inputs
+  pdl_wait();
+  pdl_launch_dependents();
+  const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  float* xs = logit + E;
+  if (pre) {
+    for (int e = threadIdx.x; e < E; e += blockDim.x) logit[e] = pre[(size_t)t * (E + 1) + e];
+    if (wg && threadIdx.x == 0) gate_out[t] = 1.0f / (1.0f + expf(-pre[(size_t)t * (E + 1) + E]));
+  } else {
+    const T* x = h + (size_t)t * ld_h;
+    for (int i = threadIdx.x; i < d; i += blockDim.x) xs[i] = to_f(x[i]);
+    __syncthreads();
+  }
+  for (int e = warp; e < E + (wg ? 1 : 0) && !pre; e += ROUTE_WARPS) {
+    float acc = route_dot(e < E ? wr + (size_t)e * d : wg, xs, d, lane);
     if (lane == 0) {
       if (e < E) logit[e] = acc;
       else gate_out[t] = 1.0f / (1.0f + expf(-acc));
@@ -96,14 +125,27 @@ __global__ void __launch_bounds__(ROUTE_WARPS * 32) moe_route_kernel(int* __rest
   for (int j = lane; j < top; j += 32) top_w[(size_t)t * top + j] /= denom;
 }
 
+// logits_ws: room for T * (E + 1) floats, or null.  With it, steps of up to 256 tokens form the logits in a launch of
+// their own over (tokens x groups of eight rows) CTAs; the result is the same either way (same sums, same order).
 extern "C" int qv_moe_route(int* top_idx, float* top_w, float* gate_out, const void* h, int ld_h, const void* wr, const void* wg,
-                            int T, int d, int E, int top, int dt, int w_dt, void* stream) {
+                            float* logits_ws, int T, int d, int E, int top, int dt, int w_dt, void* stream) {
   if (T <= 0) return 0;
   if (E <= 0 || top <= 0 || top > E || E > 8192) return QV_ERR_UNSUPPORTED;
   cudaStream_t st = (cudaStream_t)stream;
   const size_t smem = (size_t)(E + d) * sizeof(float);
   if (smem > 48 * 1024) return QV_ERR_TOO_LARGE;
-#define ROUTE(TT, TW) return qv_launch(moe_route_kernel<TT, TW>, dim3(T), dim3(ROUTE_WARPS * 32), smem, st, top_idx, top_w, gate_out, (const TT*)h, ld_h, (const TW*)wr, (const TW*)wg, d, E, top)
+  const bool split = logits_ws && T <= 256;
+  const dim3 lgrid(T, (E + (wg ? 1 : 0) + ROUTE_WARPS - 1) / ROUTE_WARPS);
+#define ROUTE(TT, TW)                                                                                                        \
+  do {                                                                                                                       \
+    if (split) {                                                                                                             \
+      const int rc = qv_launch(moe_logits_kernel<TT, TW>, lgrid, dim3(ROUTE_WARPS * 32), (size_t)d * sizeof(float), st, logits_ws, \
+                               (const TT*)h, ld_h, (const TW*)wr, (const TW*)wg, d, E);                                      \
+      if (rc) return rc;                                                                                                     \
+    }                                                                                                                        \
+    return qv_launch(moe_route_kernel<TT, TW>, dim3(T), dim3(ROUTE_WARPS * 32), smem, st, top_idx, top_w, gate_out, (const TT*)h, \
+                     ld_h, (const TW*)wr, (const TW*)wg, d, E, top, split ? (const float*)logits_ws : (const float*)nullptr); \
+  } while (0)
   if (dt == QV_DT_F32 && w_dt == QV_DT_F32) ROUTE(float, float);
   if (dt == QV_DT_BF16 && w_dt == QV_DT_BF16) ROUTE(bf16, bf16);
   if (dt == QV_DT_BF16 && w_dt == QV_DT_F32) ROUTE(bf16, float);

@@ -66,7 +66,7 @@ _ARGTYPES = {
     "qv_linear_scan_state_floats": [_I, _I, _I, _I],
     "qv_linear_scan": [_I, _V, _I, _V, _I, _I, _V, _I, _V, _I, _V, _I, _V, _I, _V, _V, _V, _F, _F, _V, _L, _V, _V, _I, _I, _I, _I, _I, _V],
     "qv_gated_group_norm": [_V, _I, _V, _I, _V, _I, _V, _I, _I, _I, _F, _I, _I, _V],
-    "qv_moe_route": [_V, _V, _V, _V, _I, _V, _V, _I, _I, _I, _I, _I, _I, _V],
+    "qv_moe_route": [_V, _V, _V, _V, _I, _V, _V, _V, _I, _I, _I, _I, _I, _I, _V],
     "qv_moe_max_tiles": [_I, _I, _I],
     "qv_moe_tile_rows": [_I],
     "qv_moe_group": [_V, _V, _V, _V, _V, _I, _I, _I, _I, _V],
@@ -421,9 +421,13 @@ def moe_route(top_idx, top_w, gate_out, h, w_router, w_gate) -> None:
     T, d = h.shape
     E, top = w_router.shape[0], top_idx.shape[1]
     assert h.stride(1) == 1 and w_router.is_contiguous() and w_router.shape[1] == d and top_idx.is_contiguous() and top_w.is_contiguous()
+    few = T <= 256                   # few tokens: the logits in a launch of their own, spread over more SMs
+    ws = torch.empty(T * (E + 1), device=h.device, dtype=torch.float32) if few else None
     rc = _lib("moe").qv_moe_route(_ptr(top_idx), _ptr(top_w), _ptr(gate_out), _ptr(h), h.stride(0), _ptr(w_router), _ptr(w_gate),
-                                  T, d, E, top, dt_code(h.dtype), dt_code(w_router.dtype), _stream())
+                                  _ptr(ws), T, d, E, top, dt_code(h.dtype), dt_code(w_router.dtype), _stream())
     _check(rc, "moe_route")
+    if few:
+        add_launches(1)
 
 
 def moe_tile_rows(tensor_cores: bool) -> int:
