@@ -446,6 +446,102 @@ extern "C" int qv_softcap(float* x, long long n, float cap, void* stream) {
   return qv_launch(softcap_kernel, dim3(blocks), dim3(256), 0, (cudaStream_t)stream, x, (size_t)n, cap);
 }
 
+// ---------------------------------------------------------------- scaled sum of two parts' outputs
+// out[t, i] (float32) = a[t, i] * sa[i] + b[t, i] * sb[i]; sa, sb (float32 [d]) and b may be null (factor one, no
+// second term): what a block that runs two parts side by side hands on when their outputs have per-feature factors.
+template <typename TA, typename TB>
+__global__ void scale_sum2_kernel(float* __restrict__ out, const TA* __restrict__ a, const float* __restrict__ sa,
+                                  const TB* __restrict__ b, const float* __restrict__ sb, size_t n, int d) {
+  pdl_wait();
+  pdl_launch_dependents();
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+    const int c = (int)(i % d);
+    float v = to_f(a[i]) * (sa ? sa[c] : 1.f);
+    if (b) v = fmaf(to_f(b[i]), sb ? sb[c] : 1.f, v);
+    out[i] = v;
+  }
+}
+
+extern "C" int qv_scale_sum2(float* out, const void* a, const float* sa, const void* b, const float* sb, int T, int d, int a_dt,
+                             int b_dt, void* stream) {
+  const size_t n = (size_t)T * d;
+  if (n == 0) return 0;
+  const int blocks = (int)((n + 255) / 256 < 148 * 16 ? (n + 255) / 256 : 148 * 16);
+  cudaStream_t st = (cudaStream_t)stream;
+#define QV_SS2(TA, TB) return qv_launch(scale_sum2_kernel<TA, TB>, dim3(blocks), dim3(256), 0, st, out, (const TA*)a, sa, (const TB*)b, sb, n, d)
+  if (a_dt == QV_DT_F32 && b_dt == QV_DT_F32) QV_SS2(float, float);
+  if (a_dt == QV_DT_BF16 && b_dt == QV_DT_BF16) QV_SS2(bf16, bf16);
+  if (a_dt == QV_DT_F32 && b_dt == QV_DT_BF16) QV_SS2(float, bf16);
+  if (a_dt == QV_DT_BF16 && b_dt == QV_DT_F32) QV_SS2(bf16, float);
+#undef QV_SS2
+  return QV_ERR_UNSUPPORTED;
+}
+
+// ---------------------------------------------------------------- re-entry of the stream: [x + delta ; x0]
+// out[t] = [residual[t] + delta[t] (float32 sum) | x0[t]] in the compute type, 2d wide: the input of the product
+// that carries the stream and the embedding's output back into a stretch of layers that runs again.
+template <typename TD, typename TO>
+__global__ void stream_concat_kernel(TO* __restrict__ out, const float* __restrict__ residual, const TD* __restrict__ delta,
+                                     const float* __restrict__ x0, size_t n, int d) {
+  pdl_wait();
+  pdl_launch_dependents();
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+    const size_t t = i / d;
+    const int c = (int)(i - t * d);
+    out[t * 2 * d + c] = from_f<TO>(residual[i] + (delta ? to_f(delta[i]) : 0.f));
+    out[t * 2 * d + d + c] = from_f<TO>(x0[i]);
+  }
+}
+
+extern "C" int qv_stream_concat(void* out, const float* residual, const void* delta, const float* x0, int T, int d, int delta_dt,
+                                int out_dt, void* stream) {
+  const size_t n = (size_t)T * d;
+  if (n == 0) return 0;
+  const int blocks = (int)((n + 255) / 256 < 148 * 16 ? (n + 255) / 256 : 148 * 16);
+  cudaStream_t st = (cudaStream_t)stream;
+#define QV_SC(TD, TO) return qv_launch(stream_concat_kernel<TD, TO>, dim3(blocks), dim3(256), 0, st, (TO*)out, residual, (const TD*)delta, x0, n, d)
+  if (delta_dt == QV_DT_F32 && out_dt == QV_DT_F32) QV_SC(float, float);
+  if (delta_dt == QV_DT_BF16 && out_dt == QV_DT_BF16) QV_SC(bf16, bf16);
+  if (delta_dt == QV_DT_F32 && out_dt == QV_DT_BF16) QV_SC(float, bf16);
+  if (delta_dt == QV_DT_BF16 && out_dt == QV_DT_F32) QV_SC(bf16, float);
+#undef QV_SC
+  return QV_ERR_UNSUPPORTED;
+}
+
+// x[t, :] += v[:] (float32), one vector for all rows.
+__global__ void add_vector_kernel(float* __restrict__ x, const float* __restrict__ v, size_t n, int d) {
+  pdl_wait();
+  pdl_launch_dependents();
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) x[i] += v[i % d];
+}
+
+extern "C" int qv_add_vector(float* x, const float* v, int T, int d, void* stream) {
+  const size_t n = (size_t)T * d;
+  if (n == 0) return 0;
+  const int blocks = (int)((n + 255) / 256 < 148 * 16 ? (n + 255) / 256 : 148 * 16);
+  return qv_launch(add_vector_kernel, dim3(blocks), dim3(256), 0, (cudaStream_t)stream, x, v, n, d);
+}
+
+// ---------------------------------------------------------------- ungated activations
+// out = act(x) elementwise in place or not; kind 0: the square of relu.
+template <typename T>
+__global__ void activation_kernel(T* __restrict__ out, const T* __restrict__ x, size_t n, int kind) {
+  pdl_wait();
+  pdl_launch_dependents();
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+    const float v = fmaxf(to_f(x[i]), 0.f);
+    out[i] = from_f<T>(v * v);
+  }
+}
+
+extern "C" int qv_activation(void* out, const void* x, long long n, int kind, int dt, void* stream) {
+  if (n <= 0) return 0;
+  if (kind != 0) return QV_ERR_UNSUPPORTED;
+  const int blocks = (int)((n + 255) / 256 < 148 * 16 ? (n + 255) / 256 : 148 * 16);
+  QV_DISPATCH_DT(dt, TT, return qv_launch(activation_kernel<TT>, dim3(blocks), dim3(256), 0, (cudaStream_t)stream, (TT*)out, (const TT*)x, (size_t)n, kind));
+  return QV_ERR_UNSUPPORTED;
+}
+
 extern "C" const char* qv_error_string(int code) {
   if (code == QV_ERR_UNSUPPORTED) return "size or dtype not supported by this kernel";
   if (code == QV_ERR_TOO_LARGE) return "size exceeds what this kernel can hold on chip";

@@ -4,14 +4,16 @@
 // qv_moe_route    logits = Wr h in float32 (fixed summation order), the `top` largest per token (ties: the lower
 //                 index), weights = softmax over the chosen logits only; optionally one more row of the router
 //                 matrix' companion (a scalar gate per token: sigmoid(ws . h)).
+// qv_moe_route_table  no router: row `token id` of an integer table [vocab, top] lists the token's experts, each weighted 1/top.
 // qv_moe_group    counting sort of the (token, choice) pairs by expert, all on the device (a step never waits
 //                 for the host): row_token[r] = token of sorted row r, slot_row[token * top + j] = its sorted row,
 //                 and a table of row tiles (expert, first row, rows) for the products' grids.
 // qv_moe_experts  CUDA-core products over the grouped rows, float32 multiply-adds with k ascending:
-//                   UP:   act[r] = silu(Wg_e h[row_token[r]]) * (Wu_e h[row_token[r]])
-//                   DOWN: y[r]   = Wd_e act[r]   (float32)
-// qv_moe_combine  delta[t] = (mixer output) + sum_j weight[t, j] * y[slot_row[t, j]] + gate[t] * shared[t]
-//                 in float32, choices summed in the order the router ranked them.
+//                   UP (1):   act[r] = silu(Wg_e h[row_token[r]]) * (Wu_e h[row_token[r]])
+//                   UP (2):   act[r] = relu(Wu_e h[row_token[r]])^2            (ungated experts)
+//                   DOWN (0): y[r]   = Wd_e act[r]   (float32)
+// qv_moe_combine  delta[t] = (mixer output) * s_mix + (sum_j weight[t, j] * y[slot_row[t, j]] + gate[t] * shared[t]) * s_ff
+//                 in float32, choices summed in the order the router ranked them; s_mix, s_ff: per-feature factors or none.
 #include "common.cuh"
 
 #define ROUTE_WARPS 8
@@ -154,6 +156,31 @@ extern "C" int qv_moe_route(int* top_idx, float* top_w, float* gate_out, const v
   return QV_ERR_UNSUPPORTED;
 }
 
+// top_idx[t][j] = table[ids[t]][j] (an entry outside 0..E-1, which a sound table has not, reads as expert 0), top_w = 1/top.
+__global__ void moe_route_table_kernel(int* __restrict__ top_idx, float* __restrict__ top_w, const int* __restrict__ table,
+                                       const int* __restrict__ ids, int n, int top, int vocab, int E) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const float w = 1.0f / (float)top;
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
+    const int t = i / top, j = i - t * top;
+    int id = ids[t];
+    if (id < 0 || id >= vocab) id = 0;
+    const int e = table[(size_t)id * top + j];
+    top_idx[i] = (e >= 0 && e < E) ? e : 0;
+    top_w[i] = w;
+  }
+}
+
+extern "C" int qv_moe_route_table(int* top_idx, float* top_w, const int* table, const int* ids, int T, int top, int vocab, int E,
+                                  void* stream) {
+  if (T <= 0) return 0;
+  if (top <= 0 || E <= 0 || top > E) return QV_ERR_UNSUPPORTED;
+  const int n = T * top;
+  const int blocks = (n + 255) / 256 < 148 * 8 ? (n + 255) / 256 : 148 * 8;
+  return qv_launch(moe_route_table_kernel, dim3(blocks), dim3(256), 0, (cudaStream_t)stream, top_idx, top_w, table, ids, n, top, vocab, E);
+}
+
 // One block.  tiles: [max_tiles][3] = (expert or -1, first sorted row, rows).
 __global__ void __launch_bounds__(1024) moe_group_kernel(int* __restrict__ row_token, int* __restrict__ slot_row, int* __restrict__ tiles,
                                                          int max_tiles, const int* __restrict__ top_idx, int* __restrict__ rank_tmp,
@@ -210,12 +237,15 @@ extern "C" int qv_moe_group(int* row_token, int* slot_row, int* tiles, const int
 }
 
 // Tile of 32 rows x 64 columns, 256 threads, each 2 rows x 4 columns; k in steps of 16, ascending.
-// UP: a = h (rows gathered by row_token), w1/w2 = gate/up matrices [E][N][K]; out act [R, N] in the compute type.
-// DOWN: a = act [R, K]; w1 = down matrices [E][N][K]; out y [R, N] float32.
-template <typename T, typename TW, bool UP>
+// MODE 1 (gated up): a = h (rows gathered by row_token), w1/w2 = gate/up matrices [E][N][K]; out act [R, N] in the compute type.
+// MODE 2 (ungated up): as 1 with w1 the up matrices alone and the square of relu as activation.
+// MODE 0 (down): a = act [R, K]; w1 = down matrices [E][N][K]; out y [R, N] float32.
+template <typename T, typename TW, int MODE>
 __global__ void __launch_bounds__(256) moe_experts_kernel(void* __restrict__ out_, int ld_out, const T* __restrict__ a, int ld_a,
                                                           const TW* __restrict__ w1, const TW* __restrict__ w2,
                                                           const int* __restrict__ row_token, const int* __restrict__ tiles, int N, int K) {
+  constexpr bool GATHER = MODE != 0;         // rows of a are gathered, the output is in the compute type
+  constexpr bool UP = MODE == 1;             // a second matrix (the gate's partner)
   __shared__ float As[MOE_BK][MOE_BM + 1];
   __shared__ float B1[MOE_BK][MOE_BN + 1];
   __shared__ float B2[UP ? MOE_BK : 1][MOE_BN + 1];
@@ -233,7 +263,7 @@ __global__ void __launch_bounds__(256) moe_experts_kernel(void* __restrict__ out
   const int ar = threadIdx.x >> 3, ak = (threadIdx.x & 7) * 2;
   size_t a_row = 0;
   const bool a_ok = ar < rows;
-  if (a_ok) a_row = UP ? (size_t)row_token[row0 + ar] : (size_t)(row0 + ar);
+  if (a_ok) a_row = GATHER ? (size_t)row_token[row0 + ar] : (size_t)(row0 + ar);
   const int bn = threadIdx.x >> 2, bk = (threadIdx.x & 3) * 4;
   for (int k0 = 0; k0 < K; k0 += MOE_BK) {
 #pragma unroll
@@ -277,6 +307,9 @@ __global__ void __launch_bounds__(256) moe_experts_kernel(void* __restrict__ out
       if (UP) {
         const float g = acc1[r][c];
         ((T*)out_)[(size_t)(row0 + row) * ld_out + n] = from_f<T>(g / (1.0f + expf(-g)) * acc2[r][c]);
+      } else if (MODE == 2) {
+        const float g = fmaxf(acc1[r][c], 0.f);
+        ((T*)out_)[(size_t)(row0 + row) * ld_out + n] = from_f<T>(g * g);
       } else {
         ((float*)out_)[(size_t)(row0 + row) * ld_out + n] = acc1[r][c];
       }
@@ -293,9 +326,11 @@ extern "C" int qv_moe_experts(int up, void* out, int ld_out, const void* a, int 
   cudaStream_t st = (cudaStream_t)stream;
 #define EXPERTS(TT, TW)                                                                                                        \
   do {                                                                                                                         \
-    if (up) return qv_launch(moe_experts_kernel<TT, TW, true>, grid, dim3(256), 0, st, out, ld_out, (const TT*)a, ld_a, (const TW*)w1, \
-                             (const TW*)w2, row_token, tiles, N, K);                                                           \
-    return qv_launch(moe_experts_kernel<TT, TW, false>, grid, dim3(256), 0, st, out, ld_out, (const TT*)a, ld_a, (const TW*)w1,  \
+    if (up == 1) return qv_launch(moe_experts_kernel<TT, TW, 1>, grid, dim3(256), 0, st, out, ld_out, (const TT*)a, ld_a, (const TW*)w1, \
+                                  (const TW*)w2, row_token, tiles, N, K);                                                      \
+    if (up == 2) return qv_launch(moe_experts_kernel<TT, TW, 2>, grid, dim3(256), 0, st, out, ld_out, (const TT*)a, ld_a, (const TW*)w1, \
+                                  (const TW*)w2, row_token, tiles, N, K);                                                      \
+    return qv_launch(moe_experts_kernel<TT, TW, 0>, grid, dim3(256), 0, st, out, ld_out, (const TT*)a, ld_a, (const TW*)w1,      \
                      (const TW*)w2, row_token, tiles, N, K);                                                                   \
   } while (0)
   if (dt == QV_DT_F32 && w_dt == QV_DT_F32) EXPERTS(float, float);
@@ -325,10 +360,12 @@ __device__ __forceinline__ void mma16816(float* c, const uint32_t* a, uint32_t b
                : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
-template <bool UP, int BK, int STAGES>
+template <int MODE, int BK, int STAGES>
 __global__ void __launch_bounds__(128) moe_experts_tc_kernel(void* __restrict__ out_, int ld_out, const bf16* __restrict__ a, int ld_a,
                                                              const bf16* __restrict__ w1, const bf16* __restrict__ w2,
                                                              const int* __restrict__ row_token, const int* __restrict__ tiles, int N, int K) {
+  constexpr bool GATHER = MODE != 0;         // modes as in moe_experts_kernel
+  constexpr bool UP = MODE == 1;
   constexpr int LD = BK + 8;                 // padded row of a staged tile: ldmatrix without bank conflicts
   constexpr int PIECES = BK / 8;             // 16-byte pieces of a row
   constexpr int TILE = 64 * LD;              // elements of one staged 64-row tile
@@ -355,7 +392,7 @@ __global__ void __launch_bounds__(128) moe_experts_tc_kernel(void* __restrict__ 
       for (int c = tid; c < 64 * PIECES; c += 128) {
         const int r = c / PIECES, pc = c - r * PIECES, k = k0 + pc * 8;
         const bool kin = k < K, aok = r < rows && kin;
-        const size_t src_row = aok ? (UP ? (size_t)row_token[row0 + r] : (size_t)(row0 + r)) : 0;
+        const size_t src_row = aok ? (GATHER ? (size_t)row_token[row0 + r] : (size_t)(row0 + r)) : 0;
         cp_async16(As + buf * TILE + r * LD + pc * 8, a + src_row * ld_a + (kin ? k : 0), aok ? 16 : 0);
         cp_async16(B1 + buf * TILE + r * LD + pc * 8, W1 + tile_off + c * 8, 16);
         if (UP) cp_async16(B2 + buf * TILE + r * LD + pc * 8, W2 + tile_off + c * 8, 16);
@@ -418,6 +455,7 @@ __global__ void __launch_bounds__(128) moe_experts_tc_kernel(void* __restrict__ 
           if (n >= N) continue;
           const float v = acc1[mt][nt][half * 2 + j];
           if (UP) ((bf16*)out_)[(size_t)(row0 + r) * ld_out + n] = __float2bfloat16_rn(v / (1.0f + expf(-v)) * acc2[mt][nt][half * 2 + j]);
+          else if (MODE == 2) ((bf16*)out_)[(size_t)(row0 + r) * ld_out + n] = __float2bfloat16_rn(fmaxf(v, 0.f) * fmaxf(v, 0.f));
           else ((float*)out_)[(size_t)(row0 + r) * ld_out + n] = v;
         }
       }
@@ -440,14 +478,19 @@ extern "C" int qv_moe_experts_tc(int up, void* out, int ld_out, const void* a, i
   // k in steps of 64 through three stages: a row of a weight tile is then a whole 128-byte line and two stages of
   // copies are in flight while one is multiplied
   constexpr int BK = 64, STAGES = 3;
-  const size_t smem = (size_t)STAGES * 64 * (BK + 8) * 2 * (up ? 3 : 2);
-  if (up) {
-    cudaFuncSetAttribute(moe_experts_tc_kernel<true, BK, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    return qv_launch(moe_experts_tc_kernel<true, BK, STAGES>, grid, dim3(128), smem, st, out, ld_out, (const bf16*)a, ld_a, (const bf16*)w1,
+  const size_t smem = (size_t)STAGES * 64 * (BK + 8) * 2 * (up == 1 ? 3 : 2);
+  if (up == 1) {
+    cudaFuncSetAttribute(moe_experts_tc_kernel<1, BK, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    return qv_launch(moe_experts_tc_kernel<1, BK, STAGES>, grid, dim3(128), smem, st, out, ld_out, (const bf16*)a, ld_a, (const bf16*)w1,
                      (const bf16*)w2, row_token, tiles, N, K);
   }
-  cudaFuncSetAttribute(moe_experts_tc_kernel<false, BK, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-  return qv_launch(moe_experts_tc_kernel<false, BK, STAGES>, grid, dim3(128), smem, st, out, ld_out, (const bf16*)a, ld_a, (const bf16*)w1,
+  if (up == 2) {
+    cudaFuncSetAttribute(moe_experts_tc_kernel<2, BK, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    return qv_launch(moe_experts_tc_kernel<2, BK, STAGES>, grid, dim3(128), smem, st, out, ld_out, (const bf16*)a, ld_a, (const bf16*)w1,
+                     (const bf16*)w2, row_token, tiles, N, K);
+  }
+  cudaFuncSetAttribute(moe_experts_tc_kernel<0, BK, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  return qv_launch(moe_experts_tc_kernel<0, BK, STAGES>, grid, dim3(128), smem, st, out, ld_out, (const bf16*)a, ld_a, (const bf16*)w1,
                    (const bf16*)w2, row_token, tiles, N, K);
 }
 
@@ -455,7 +498,8 @@ extern "C" int qv_moe_experts_tc(int up, void* out, int ld_out, const void* a, i
 template <typename T>
 __global__ void __launch_bounds__(256) moe_combine_kernel(float* __restrict__ delta, const T* __restrict__ mix, const float* __restrict__ y,
                                                           const int* __restrict__ slot_row, const float* __restrict__ top_w,
-                                                          const T* __restrict__ shared, const float* __restrict__ gate, int d, int top) {
+                                                          const T* __restrict__ shared, const float* __restrict__ gate, int d, int top,
+                                                          const float* __restrict__ s_mix, const float* __restrict__ s_ff) {
   pdl_wait();
   pdl_launch_dependents();
   const int t = blockIdx.x;
@@ -465,16 +509,18 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(float* __restrict__ de
     for (int j = 0; j < top; ++j) routed = fmaf(top_w[(size_t)t * top + j], y[(size_t)slot_row[(size_t)t * top + j] * d + i], routed);
     float v = routed;
     if (shared) v = fmaf(g, to_f(shared[(size_t)t * d + i]), v);
-    if (mix) v += to_f(mix[(size_t)t * d + i]);
+    if (s_ff) v *= s_ff[i];
+    if (mix) v = fmaf(to_f(mix[(size_t)t * d + i]), s_mix ? s_mix[i] : 1.f, v);
     delta[(size_t)t * d + i] = v;
   }
 }
 
 extern "C" int qv_moe_combine(float* delta, const void* mix, const float* y, const int* slot_row, const float* top_w,
-                              const void* shared, const float* gate, int T, int d, int top, int dt, void* stream) {
+                              const void* shared, const float* gate, int T, int d, int top, int dt, const float* s_mix,
+                              const float* s_ff, void* stream) {
   if (T <= 0) return 0;
   QV_DISPATCH_DT(dt, TT,
                  return qv_launch(moe_combine_kernel<TT>, dim3(T, T < 256 ? (d + 255) / 256 : 1), dim3(256), 0, (cudaStream_t)stream, delta, (const TT*)mix, y, slot_row,
-                                  top_w, (const TT*)shared, gate, d, top));
+                                  top_w, (const TT*)shared, gate, d, top, s_mix, s_ff));
   return QV_ERR_UNSUPPORTED;
 }

@@ -72,7 +72,14 @@ _ARGTYPES = {
     "qv_moe_group": [_V, _V, _V, _V, _V, _I, _I, _I, _I, _V],
     "qv_moe_experts_tc": [_I, _V, _I, _V, _I, _V, _V, _V, _V, _I, _I, _I, _I, _V],
     "qv_moe_experts": [_I, _V, _I, _V, _I, _V, _V, _V, _V, _I, _I, _I, _I, _I, _I, _V],
-    "qv_moe_combine": [_V, _V, _V, _V, _V, _V, _V, _I, _I, _I, _I, _V],
+    "qv_moe_combine": [_V, _V, _V, _V, _V, _V, _V, _I, _I, _I, _I, _V, _V, _V],
+    "qv_moe_route_table": [_V, _V, _V, _V, _I, _I, _I, _I, _V],
+    "qv_scale_sum2": [_V, _V, _V, _V, _V, _I, _I, _I, _I, _V],
+    "qv_stream_concat": [_V, _V, _V, _V, _I, _I, _I, _I, _V],
+    "qv_add_vector": [_V, _V, _I, _I, _V],
+    "qv_activation": [_V, _V, _L, _I, _I, _V],
+    "qv_diff_prepare": [_V, _I, _V, _I, _V, _V, _V, _F, _V, _I, _V, _V, _V, _I, _V, _I, _I, _I, _I, _I, _I, _I, _I, _I, _V],
+    "qv_diff_attention_generic": [_V, _I, _V, _I, _V, _V, _V, _V, _I, _I, _I, _I, _I, _I, _I, _I, _F, _F, _F, _F, _I, _V],
     "qv_argmax": [_V, _V, _I, _I, _L, _V],
     "qv_sample": [_V, _V, _I, _I, _L, _V, _V, _V, _V, _V, _V, _I, _V, _V, _V, _V],
 }
@@ -275,6 +282,90 @@ def softcap(x, cap: float) -> None:
     _check(_lib("elementwise").qv_softcap(_ptr(x), x.numel(), float(cap), _stream()), "softcap")
 
 
+def scale_sum2(out, a, sa, b=None, sb=None) -> None:
+    """out (float32 [T, d]) = a * sa + b * sb with per-feature factors sa, sb (float32 [d] or None); b may be None."""
+    _need_cuda(out, a, sa, b, sb)
+    T, d = out.shape
+    assert out.dtype == torch.float32 and out.is_contiguous() and a.is_contiguous() and a.shape == out.shape
+    assert b is None or (b.is_contiguous() and b.shape == out.shape)
+    for sc in (sa, sb):
+        assert sc is None or (sc.dtype == torch.float32 and sc.is_contiguous() and sc.numel() == d)
+    rc = _lib("elementwise").qv_scale_sum2(_ptr(out), _ptr(a), _ptr(sa), _ptr(b), _ptr(sb), T, d, dt_code(a.dtype),
+                                           dt_code(b.dtype) if b is not None else dt_code(a.dtype), _stream())
+    _check(rc, "scale_sum2")
+
+
+def stream_concat(out, residual, delta, x0) -> None:
+    """out [T, 2d] (compute type) = [residual + delta (float32 sum; delta may be None) | x0], residual and x0 float32 [T, d]."""
+    _need_cuda(out, residual, delta, x0)
+    T, d = residual.shape
+    assert out.shape == (T, 2 * d) and out.is_contiguous() and residual.dtype == x0.dtype == torch.float32
+    assert residual.is_contiguous() and x0.is_contiguous() and x0.shape == residual.shape
+    assert delta is None or (delta.is_contiguous() and delta.shape == residual.shape)
+    rc = _lib("elementwise").qv_stream_concat(_ptr(out), _ptr(residual), _ptr(delta), _ptr(x0), T, d,
+                                              dt_code(delta.dtype) if delta is not None else F32, dt_code(out.dtype), _stream())
+    _check(rc, "stream_concat")
+
+
+def add_vector(x, v) -> None:
+    """x[t, :] += v (both float32), in place."""
+    _need_cuda(x, v)
+    assert x.dtype == v.dtype == torch.float32 and x.is_contiguous() and v.is_contiguous() and v.numel() == x.shape[1]
+    _check(_lib("elementwise").qv_add_vector(_ptr(x), _ptr(v), x.shape[0], x.shape[1], _stream()), "add_vector")
+
+
+ACT_RELU2 = 0
+
+
+def activation(out, x, kind: int = ACT_RELU2) -> None:
+    """out = act(x) elementwise (out may be x); kind ACT_RELU2: the square of relu."""
+    _need_cuda(out, x)
+    assert out.dtype == x.dtype and out.is_contiguous() and x.is_contiguous() and out.numel() == x.numel()
+    _check(_lib("elementwise").qv_activation(_ptr(out), _ptr(x), x.numel(), kind, dt_code(x.dtype), _stream()), "activation")
+
+
+# ------------------------------------------------------------------ differential attention
+
+def diff_prepare(q_out, proj, bias, q_weight, k_weight, eps, cos_sin, ctx, block_table, cache_layer, H, G, n, dv, rot, page) -> None:
+    """Per token of proj (float32 or the compute type; columns [q: H*2n | k: G*2n | v: G*dv]): bias added, every map of q and
+    k RMS-normed over n with its weight and rotated over its first `rot` entries (pairs i, i + rot/2); q -> q_out [T, H*2n],
+    k and v -> the token's row of cache_layer [pages, page, G*(2n+dv)]."""
+    _need_cuda(q_out, proj, bias, q_weight, k_weight, cos_sin, block_table, cache_layer)
+    T = proj.shape[0]
+    assert proj.stride(1) == 1 and proj.shape[1] == (H + G) * 2 * n + G * dv and q_out.stride(1) == 1 and q_out.shape == (T, H * 2 * n)
+    assert cache_layer.is_contiguous() and tuple(cache_layer.shape[1:]) == (page, G * (2 * n + dv)) and cache_layer.dtype == q_out.dtype
+    assert q_weight.dtype == k_weight.dtype == torch.float32 and q_weight.numel() == k_weight.numel() == n
+    assert bias is None or (bias.dtype == torch.float32 and bias.is_contiguous() and bias.numel() == proj.shape[1])
+    if rot:
+        assert cos_sin.dtype == torch.float32 and cos_sin.is_contiguous() and cos_sin.shape[1] * 2 == rot
+    _i32(block_table, "block_table")
+    rc = _lib("diff_attention").qv_diff_prepare(
+        _ptr(q_out), q_out.stride(0), _ptr(proj), proj.stride(0), _ptr(bias), _ptr(q_weight), _ptr(k_weight), float(eps), _ptr(cos_sin),
+        cos_sin.shape[0] if cos_sin is not None else 1, _ptr(ctx.tok_pos), _ptr(ctx.tok_seg), _ptr(block_table), block_table.shape[-1],
+        _ptr(cache_layer), T, H, G, n, dv, rot, page, dt_code(proj.dtype), dt_code(q_out.dtype), _stream())
+    _check(rc, "diff_prepare")
+
+
+def diff_attention_generic(out, q, cache_layer, ctx, block_table, H, G, n, dv, page, window, scale, lam, eps, post) -> None:
+    """out[t, h*dv:(h+1)*dv] = (a1 - lam * a2) / rms * post for every token and head, a1 and a2 the head's two softmax
+    maps over its request's cache rows; float32 arithmetic, any sizes (value size up to 512)."""
+    _need_cuda(out, q, cache_layer, block_table)
+    T = q.shape[0]
+    assert q.stride(1) == 1 and out.stride(1) == 1 and q.dtype == out.dtype == cache_layer.dtype
+    assert cache_layer.is_contiguous() and tuple(cache_layer.shape[1:]) == (page, G * (2 * n + dv))
+    _i32(block_table, "block_table")
+    rc = _lib("diff_attention").qv_diff_attention_generic(
+        _ptr(out), out.stride(0), _ptr(q), q.stride(0), _ptr(cache_layer), _ptr(ctx.tok_pos), _ptr(ctx.tok_seg), _ptr(block_table),
+        block_table.shape[-1], T, H, G, n, dv, page, int(window), float(scale), float(lam), float(eps), float(post), dt_code(q.dtype),
+        _stream())
+    _check(rc, "diff_attention_generic")
+
+
+def diff_attention(out, q, cache_layer, ctx, block_table, H, G, n, dv, page, window, scale, lam, eps, post) -> None:
+    """Differential attention of every token of the step over its request's cache rows."""
+    diff_attention_generic(out, q, cache_layer, ctx, block_table, H, G, n, dv, page, window, scale, lam, eps, post)
+
+
 # ------------------------------------------------------------------ latent attention
 
 def latent_prepare(proj, q_off: int, kv_off: int, cache_layer, norm_w, eps, cos_sin, ctx, block_table, H, dn, dr, rank, rot, page) -> None:
@@ -458,8 +549,8 @@ def moe_pack_experts(w: torch.Tensor) -> torch.Tensor:
     return w.view(E, Np // 64, 64, Kp // 64, 64).permute(0, 1, 3, 2, 4).contiguous()
 
 
-def moe_experts_tc(up: bool, out, a, p1, p2, row_token, tiles) -> None:
-    """The experts' products on the tensor cores (bfloat16).  p1, p2: matrices packed by moe_pack_experts; the sizes
+def moe_experts_tc(up, out, a, p1, p2, row_token, tiles) -> None:
+    """The experts' products on the tensor cores (bfloat16); up as for moe_experts.  p1, p2: matrices packed by moe_pack_experts; the sizes
     follow from out [R, N] and a [., K]; the tile table was made for tiles of moe_tile_rows(True) rows."""
     _need_cuda(out, a, p1, p2, row_token, tiles)
     R, N = out.shape
@@ -468,35 +559,50 @@ def moe_experts_tc(up: bool, out, a, p1, p2, row_token, tiles) -> None:
     assert a.dtype == p1.dtype == torch.bfloat16 and a.stride(1) == 1 and out.stride(1) == 1 and a.stride(0) % 8 == 0
     assert p1.is_contiguous() and tuple(p1.shape[1:]) == (-(-N // 64), -(-K // 64), 64, 64) and R == row_token.numel()
     assert out.dtype == (torch.bfloat16 if up else torch.float32)
-    rc = _lib("moe").qv_moe_experts_tc(1 if up else 0, _ptr(out), out.stride(0), _ptr(a), a.stride(0), _ptr(p1), _ptr(p2),
+    rc = _lib("moe").qv_moe_experts_tc(int(up), _ptr(out), out.stride(0), _ptr(a), a.stride(0), _ptr(p1), _ptr(p2),
                                        _ptr(row_token), _ptr(tiles), R, E, N, K, _stream())
     _check(rc, "moe_experts_tc")
 
 
-def moe_experts(up: bool, out, a, w1, w2, row_token, tiles) -> None:
+def moe_experts(up, out, a, w1, w2, row_token, tiles) -> None:
     """The experts' products over the grouped rows on the CUDA cores (float32 multiply-adds, k ascending).
-    up: out[r] = silu(w1[e] x) * (w2[e] x) with x = a[row_token[r]]; else out[r] (float32) = w1[e] a[r].
+    up True or 1: out[r] = silu(w1[e] x) * (w2[e] x) with x = a[row_token[r]]; 2: out[r] = relu(w1[e] x)^2 (ungated
+    experts, w2 None); False or 0: out[r] (float32) = w1[e] a[r].
     w1, w2: [E, N, K]; the tile table was made for tiles of moe_tile_rows(False) rows."""
     _need_cuda(out, a, w1, w2, row_token, tiles)
     R = row_token.numel()
     E, N, K = w1.shape
     assert w1.is_contiguous() and a.stride(1) == 1 and out.stride(1) == 1 and a.shape[1] == K and out.shape == (R, N)
     assert out.dtype == (a.dtype if up else torch.float32)
-    rc = _lib("moe").qv_moe_experts(1 if up else 0, _ptr(out), out.stride(0), _ptr(a), a.stride(0), _ptr(w1), _ptr(w2),
+    rc = _lib("moe").qv_moe_experts(int(up), _ptr(out), out.stride(0), _ptr(a), a.stride(0), _ptr(w1), _ptr(w2),
                                     _ptr(row_token), _ptr(tiles), R, E, N, K, dt_code(a.dtype), dt_code(w1.dtype), _stream())
     _check(rc, "moe_experts")
 
 
-def moe_combine(delta, mix, y, slot_row, top_w, shared, gate) -> None:
-    """delta (float32) = mix + sum_j top_w[t, j] * y[slot_row[t, j]] + gate[t] * shared[t]; mix, shared, gate may be None."""
-    _need_cuda(delta, mix, y, slot_row, top_w, shared, gate)
+def moe_route_table(top_idx, top_w, table, ids, experts: int) -> None:
+    """Experts without a router: top_idx[t] = table[ids[t]] (int32 [vocab, top]), top_w = 1/top."""
+    _need_cuda(top_idx, top_w, table, ids)
+    _i32(table, "table"); _i32(ids, "ids"); _i32(top_idx, "top_idx")
+    T, top = top_idx.shape
+    assert table.shape[1] == top and top_w.is_contiguous() and top_w.dtype == torch.float32 and ids.numel() >= T
+    rc = _lib("moe").qv_moe_route_table(_ptr(top_idx), _ptr(top_w), _ptr(table), _ptr(ids), T, top, table.shape[0], int(experts), _stream())
+    _check(rc, "moe_route_table")
+
+
+def moe_combine(delta, mix, y, slot_row, top_w, shared, gate, mix_scale=None, ff_scale=None) -> None:
+    """delta (float32) = mix * mix_scale + (sum_j top_w[t, j] * y[slot_row[t, j]] + gate[t] * shared[t]) * ff_scale; mix,
+    shared, gate and the per-feature scales (float32 [d]) may be None."""
+    _need_cuda(delta, mix, y, slot_row, top_w, shared, gate, mix_scale, ff_scale)
+    for sc in (mix_scale, ff_scale):
+        assert sc is None or (sc.dtype == torch.float32 and sc.is_contiguous() and sc.numel() == delta.shape[1])
     T, d = delta.shape
     assert delta.dtype == torch.float32 and delta.is_contiguous() and y.dtype == torch.float32 and y.is_contiguous()
     ref = mix if mix is not None else shared
     for t in (mix, shared):
         assert t is None or (t.is_contiguous() and t.shape == delta.shape and t.dtype == ref.dtype)
     rc = _lib("moe").qv_moe_combine(_ptr(delta), _ptr(mix), _ptr(y), _ptr(slot_row), _ptr(top_w), _ptr(shared), _ptr(gate), T, d,
-                                    top_w.shape[1], dt_code(ref.dtype) if ref is not None else F32, _stream())
+                                    top_w.shape[1], dt_code(ref.dtype) if ref is not None else F32, _ptr(mix_scale), _ptr(ff_scale),
+                                    _stream())
     _check(rc, "moe_combine")
 
 

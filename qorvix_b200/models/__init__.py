@@ -1,3 +1,4 @@
 from . import llama          # registers "LlamaForCausalLM"
 from . import deganex        # registers "Deganex"
+from . import lotirax        # registers "Lotirax"
 from .text_model import TextModel

@@ -30,6 +30,9 @@ class TextModel:
         self.final_norm = build_part("norm", spec.final_norm, source, rt)
         self.lm_head = Linear(source.get(spec.lm_head)) if spec.lm_head is not None else Linear(self.embedding)
         self.order: List[int] = list(spec.order)
+        # a stretch of layers that runs again: where the stream re-enters it (None: no such stretch)
+        self.loop = build_part("stream", getattr(spec, "loop", None), source, rt)
+        self.stream_tap = None         # callable(run, residual, pending) after every run: for tests and debugging
         self._native = None            # the native executor of this model over a cache, made on first use (False: not applicable)
 
     def cache_needs(self):
@@ -69,12 +72,20 @@ class TextModel:
         else:
             ops.embed(residual, self.embedding, ctx.token_ids)
         pending = None
+        x0 = None
+        if self.loop is not None:                  # the embedding's output, kept for the passes' re-entries
+            x0 = torch.empty_like(residual)
+            ops.cast_rows(x0, residual)
         for run, li in enumerate(self.order):
+            if self.loop is not None and run in self.loop.pass_of:
+                residual, pending = self.loop.forward(run, residual, pending, x0), None
             # which norm reads the stream after this block (a block that can prepares that norm's input);
             # none after the last block: the final norm gathers the wanted rows
             nxt = self.blocks[self.order[run + 1]] if run + 1 < len(self.order) else None
             ctx.next_norm = nxt.first_norm() if hasattr(nxt, "first_norm") else None
             residual, pending = self.blocks[li].forward(residual, pending, ctx, cache.layer_view(run))
+            if self.stream_tap is not None:
+                self.stream_tap(run, residual, pending)
         if ctx.num_wanted == 0:
             return None
         h = self.final_norm.add_norm(residual, pending, rows=ctx.want_rows)
@@ -91,3 +102,5 @@ class _BlockView:
         self.kind = layer.block
         self.mixer, self.feed_forward = layer.mixer, layer.feed_forward
         self.mixer_norm, self.ffn_norm = layer.mixer_norm, layer.ffn_norm
+        self.mixer_scale, self.ffn_scale = getattr(layer, "mixer_scale", None), getattr(layer, "ffn_scale", None)
+        self.residual_mult = getattr(layer, "residual_mult", 1.0)

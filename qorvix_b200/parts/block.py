@@ -62,22 +62,41 @@ def _folds(norm) -> bool:
 
 class ParallelBlock(Block):
     """x += mixer(norm_a(x)) + feed_forward(norm_b(x)): both parts read the stream as it enters the block.
-    When both norms are RMS norms of one eps their rows share the root mean square and come from one pass."""
+    When both norms are RMS norms of one eps their rows share the root mean square and come from one pass; a
+    block without a second norm gives both parts the one normed input.  With per-feature factors s1, s2 of the
+    parts' outputs and a multiplier m the block adds m * (s1 * mixer + s2 * feed_forward); m is folded into the
+    factors when the block is built, and the sum is formed in float32."""
 
     def __init__(self, spec, source, rt):
         self.rt = rt
         self.mixer_norm = build_part("norm", spec.mixer_norm, source, rt)
         self.mixer = build_part("mixer", spec.mixer, source, rt)
         self.feed_forward = build_part("feed_forward", spec.feed_forward, source, rt)
-        self.ffn_norm = build_part("norm", spec.ffn_norm, source, rt) if self.feed_forward is not None else None
+        self.ffn_norm = build_part("norm", getattr(spec, "ffn_norm", None), source, rt) if self.feed_forward is not None else None
+        mult = float(getattr(spec, "residual_mult", 1.0))
+        names = (getattr(spec, "mixer_scale", None), getattr(spec, "ffn_scale", None))
+        self.scaled = mult != 1.0 or any(n is not None for n in names)
+        self.mixer_scale = self.ffn_scale = None
+        if self.scaled:
+            width = self.mixer_norm.size
+            s1, s2 = (source.get(n, dtype=torch.float32) if n is not None else torch.ones(width, device=rt.device, dtype=torch.float32)
+                      for n in names)
+            self.mixer_scale, self.ffn_scale = (s1 * mult).contiguous(), (s2 * mult).contiguous()
 
     def forward(self, residual, pending, ctx, cache):
         if isinstance(pending, PreNormed):
             pending = None                       # the product is in the stream already
         a, b = self.mixer_norm, self.ffn_norm
+        if self.feed_forward is None:
+            mixed = self.mixer.forward(a.add_norm(residual, pending), ctx, cache)
+            if not self.scaled:
+                return residual, mixed
+            delta = torch.empty(residual.shape, device=residual.device, dtype=torch.float32)
+            ops.scale_sum2(delta, mixed, self.mixer_scale)
+            return residual, delta
         if b is None:
-            return residual, self.mixer.forward(a.add_norm(residual, pending), ctx, cache)
-        if _folds(a) and _folds(b) and a.eps == b.eps and a.size == b.size:
+            h1 = h2 = a.add_norm(residual, pending)
+        elif _folds(a) and _folds(b) and a.eps == b.eps and a.size == b.size:
             h1 = torch.empty((residual.shape[0], a.size), device=residual.device, dtype=self.rt.dtype)
             h2 = torch.empty_like(h1)
             ops.add_rmsnorm2(h1, h2, residual, pending, a.scale_weight(), b.scale_weight(), a.eps)
@@ -86,10 +105,15 @@ class ParallelBlock(Block):
             h2 = b.add_norm(residual, None)
         mixed = self.mixer.forward(h1, ctx, cache)
         if getattr(self.feed_forward, "takes_addend", False):
+            if self.scaled:
+                return residual, self.feed_forward.forward(h2, ctx, add=mixed, add_scale=self.mixer_scale, scale=self.ffn_scale)
             return residual, self.feed_forward.forward(h2, ctx, add=mixed)
         fed = self.feed_forward.forward(h2, ctx)
         delta = torch.empty(residual.shape, device=residual.device, dtype=torch.float32)
-        ops.sum2(delta, mixed, fed)
+        if self.scaled:
+            ops.scale_sum2(delta, mixed, self.mixer_scale, fed, self.ffn_scale)
+        else:
+            ops.sum2(delta, mixed, fed)
         return residual, delta
 
     def first_norm(self):

@@ -56,4 +56,21 @@ class SwiGLU(FeedForward):
         return self.down(act, out_dtype=self.rt.dtype)
 
 
+class ActMLP(FeedForward):
+    """Ungated feed-forward: down(act(up x)), the activation (the square of relu) as a pass of its own."""
+
+    def __init__(self, spec, source, rt):
+        if spec.activation != "relu2":
+            raise ValueError(f"unknown activation '{spec.activation}' (known: relu2)")
+        self.rt = rt
+        self.up = Linear(source.get(spec.up_proj))
+        self.down = Linear(source.get(spec.down_proj))
+
+    def forward(self, x, ctx):
+        act = self.up(x, out_dtype=self.rt.dtype)
+        ops.activation(act, act, ops.ACT_RELU2)
+        return self.down(act, out_dtype=self.rt.dtype)
+
+
 register_part("feed_forward", "swiglu", SwiGLU)
+register_part("feed_forward", "act_mlp", ActMLP)

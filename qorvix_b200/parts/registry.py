@@ -7,7 +7,7 @@ from __future__ import annotations
 
 from typing import Callable, Dict
 
-CATEGORIES = ("mixer", "feed_forward", "norm", "position", "block", "embedding")
+CATEGORIES = ("mixer", "feed_forward", "norm", "position", "block", "embedding", "stream")
 _PARTS: Dict[str, Dict[str, Callable]] = {c: {} for c in CATEGORIES}
 
 

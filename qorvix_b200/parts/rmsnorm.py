@@ -1,5 +1,5 @@
-"""RMSNorm: out = (x * 1/sqrt(mean(x^2) + eps)) * w, no bias, no 1+w
-(reference: runtime/src/ops.cpp:8-13).  The residual sum that precedes it is fused in: the
+"""RMSNorm: out = (x * 1/sqrt(mean(x^2) + eps)) * w, no bias (reference: runtime/src/ops.cpp:8-13); a spec
+with `one_plus` stores its weight around zero and the rows are scaled by 1 + w (formed once, in float32).  The residual sum that precedes it is fused in: the
 residual stream is float32 and the delta is added in float32 in the same pass."""
 from __future__ import annotations
 
@@ -15,6 +15,8 @@ class RMSNorm(Norm):
         self.eps = float(spec.eps)
         self.size = int(spec.size)
         self.weight = source.get(spec.weight, dtype=torch.float32)   # tiny; always read as float32
+        if getattr(spec, "one_plus", False):
+            self.weight = (self.weight.double() + 1.0).float()       # exact: a bfloat16 value plus one fits float32's 24 bits or rounds once
         self.rt = rt
 
     folds_into_products = True         # x * rsqrt(mean(x^2) + eps) * weight

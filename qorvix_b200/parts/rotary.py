@@ -17,6 +17,27 @@ import torch
 from ..csrc import ops
 from .base import PositionEncoding
 from .registry import register_part
+from .spec import YarnScaling
+
+
+def yarn_frequencies(rotary_dim: int, theta: float, sc) -> torch.Tensor:
+    """Frequencies under a YarnScaling: pair i keeps f_i below index lo, takes f_i / factor above index hi and a
+    linear blend between, lo and hi being the (fractional) pair indices whose waves turn `fast` and `slow`
+    times over the original length, rounded outwards and kept inside the rotated entries."""
+    i = torch.arange(rotary_dim // 2, dtype=torch.float64)
+    f = torch.exp(-(2.0 * i / rotary_dim) * math.log(theta))
+
+    def index_of(turns: float) -> float:
+        return rotary_dim * math.log(float(sc.original) / (2.0 * math.pi * turns)) / (2.0 * math.log(theta))
+
+    lo = max(math.floor(index_of(float(sc.fast))), 0)
+    hi = min(math.ceil(index_of(float(sc.slow))), rotary_dim - 1)
+    ramp = torch.clamp((i - lo) / max(hi - lo, 0.001), 0.0, 1.0)
+    return f / float(sc.factor) * ramp + f * (1.0 - ramp)
+
+
+def yarn_magnitude(sc) -> float:
+    return 0.1 * math.log(float(sc.factor)) + 1.0
 
 
 def inverse_frequencies(rotary_dim: int, theta: float, scaling=None) -> torch.Tensor:
@@ -24,6 +45,8 @@ def inverse_frequencies(rotary_dim: int, theta: float, scaling=None) -> torch.Te
     f = torch.exp(-(2.0 * i / rotary_dim) * math.log(theta))
     if scaling is None:
         return f
+    if isinstance(scaling, YarnScaling):
+        return yarn_frequencies(rotary_dim, theta, scaling)
     orig = float(scaling.original_max_position_embeddings)
     low, high, factor = float(scaling.low_freq_factor), float(scaling.high_freq_factor), float(scaling.factor)
     wavelen = 2.0 * math.pi / f
@@ -42,7 +65,8 @@ class RotaryEmbedding(PositionEncoding):
         self.inv_freq = inverse_frequencies(self.rotary_dim, float(spec.theta), spec.scaling)
         pos = torch.arange(rt.max_positions, dtype=torch.float64)
         ang = pos[:, None] * self.inv_freq[None, :]
-        self.cos_sin = torch.stack([torch.cos(ang), torch.sin(ang)], dim=-1).to(torch.float32).contiguous().to(rt.device)
+        mag = yarn_magnitude(spec.scaling) if isinstance(spec.scaling, YarnScaling) else 1.0
+        self.cos_sin = (torch.stack([torch.cos(ang), torch.sin(ang)], dim=-1) * mag).to(torch.float32).contiguous().to(rt.device)
 
     def table(self):
         return self.cos_sin

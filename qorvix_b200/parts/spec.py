@@ -14,13 +14,25 @@ TensorTable = Dict[str, Tuple[Tuple[int, ...], str]]
 
 
 @dataclass(frozen=True)
+class YarnScaling:
+    """Stretching of rotary frequencies for contexts beyond the trained length: pairs whose waves turn more
+    than `fast` times over `original` positions keep their frequency, those that turn fewer than `slow`
+    times are slowed by `factor`, those between blend linearly over the pair index; cosine and sine are
+    both multiplied by 0.1 ln(factor) + 1."""
+    factor: float
+    original: float
+    fast: float
+    slow: float
+
+
+@dataclass(frozen=True)
 class RotarySpec:
     """Rotary position encoding.  `rotary_dim` leading dims of each head are rotated in
     split-half pairs (i, i + rotary_dim/2); the reference's NeoX mode (runtime/src/ops.cpp:141-146)."""
     head_dim: int
     rotary_dim: int
     theta: float
-    scaling: Optional[object] = None          # config.RopeScaling or None
+    scaling: Optional[object] = None          # config.RopeScaling (llama3 rule), YarnScaling, or None
     kind: str = "rotary"
     pairing: str = "split_half"               # "interleaved": entry 2i is paired with 2i+1 (mixers that rotate themselves)
 
@@ -34,9 +46,10 @@ class RMSNormSpec:
     eps: float
     weight: str
     kind: str = "rmsnorm"
+    one_plus: bool = False                    # the stored weight lies around zero: the rows are scaled by 1 + w
 
     def tensors(self) -> TensorTable:
-        return {self.weight: ((self.size,), "norm")}
+        return {self.weight: ((self.size,), "normal:0:0.1" if self.one_plus else "norm")}
 
 
 @dataclass(frozen=True)
@@ -241,21 +254,136 @@ class MoESpec:
 
 
 @dataclass(frozen=True)
+class DiffAttentionSpec:
+    """Causal grouped-query differential attention: every head has two query/key maps of `head_dim` entries
+    each over the head's one set of values; the head's output is map 1 minus `lam` times map 2 (lam =
+    exp(lq1 . lk1) - exp(lq2 . lk2) + diff, one number a layer), divided by its root mean square over
+    `value_dim` and scaled by 1 - diff.  q, k and v have biases; each map of q and k is RMS-normed over
+    head_dim with a weight shared by heads and maps, then rotated."""
+    hidden_size: int
+    num_heads: int
+    num_kv_heads: int
+    head_dim: int                 # entries of one map of a head's query or key
+    value_dim: int
+    scale: float
+    diff: float
+    eps: float
+    q_proj: str                   # [heads * 2 * head_dim, hidden], head by head [map 1 | map 2]; bias: name + ".b"
+    k_proj: str
+    v_proj: str
+    q_norm: str
+    k_norm: str
+    lam_q1: str
+    lam_k1: str
+    lam_q2: str
+    lam_k2: str
+    o_proj: str
+    position: Optional[object] = None
+    window: int = 0
+    kind: str = "diff_attention"
+
+    def tensors(self) -> TensorTable:
+        H, G, n, dv, d = self.num_heads, self.num_kv_heads, self.head_dim, self.value_dim, self.hidden_size
+        t: TensorTable = {self.q_proj: ((H * 2 * n, d), "matrix"), self.q_proj + ".b": ((H * 2 * n,), "normal:0:0.02"),
+                          self.k_proj: ((G * 2 * n, d), "matrix"), self.k_proj + ".b": ((G * 2 * n,), "normal:0:0.02"),
+                          self.v_proj: ((G * dv, d), "matrix"), self.v_proj + ".b": ((G * dv,), "normal:0:0.02"),
+                          self.q_norm: ((n,), "norm"), self.k_norm: ((n,), "norm"),
+                          self.o_proj: ((d, H * dv), "matrix")}
+        for name in (self.lam_q1, self.lam_k1, self.lam_q2, self.lam_k2):
+            t[name] = ((n,), "normal:0:0.1")
+        if self.position is not None:
+            t.update(self.position.tensors())
+        return t
+
+
+@dataclass(frozen=True)
+class ActMLPSpec:
+    """Ungated feed-forward: down(act(up x)), no biases; act 'relu2' is the square of relu."""
+    hidden_size: int
+    intermediate_size: int
+    up_proj: str
+    down_proj: str
+    activation: str = "relu2"
+    kind: str = "act_mlp"
+
+    def tensors(self) -> TensorTable:
+        return {self.up_proj: ((self.intermediate_size, self.hidden_size), "matrix"),
+                self.down_proj: ((self.hidden_size, self.intermediate_size), "matrix")}
+
+
+@dataclass(frozen=True)
+class TableMoESpec:
+    """Small ungated experts (down(act(up x))) chosen without a router: row `token id` of an integer table
+    [vocab, top] lists the token's experts (the entries of a row differ), each weighted 1/top; optionally a
+    shared expert of the same form for every token, added as it is."""
+    hidden_size: int
+    vocab_size: int
+    experts: int
+    top: int
+    expert_ff: int
+    table: str
+    expert_prefix: str            # expert e's matrices are <prefix><e>.up / .down
+    shared: Optional[ActMLPSpec] = None
+    activation: str = "relu2"
+    kind: str = "table_moe"
+
+    def expert_names(self, e: int):
+        p = f"{self.expert_prefix}{e}."
+        return p + "up", p + "down"
+
+    def tensors(self) -> TensorTable:
+        t: TensorTable = {self.table: ((self.vocab_size, self.top), f"choices:{self.experts}")}
+        for e in range(self.experts):
+            u, dn = self.expert_names(e)
+            t[u] = ((self.expert_ff, self.hidden_size), "matrix")
+            t[dn] = ((self.hidden_size, self.expert_ff), "matrix")
+        if self.shared is not None:
+            t.update(self.shared.tensors())
+        return t
+
+
+@dataclass(frozen=True)
+class LoopSpec:
+    """Re-entry of the residual stream at the start of each pass over a stretch of layers that runs several
+    times: before run `first_runs[t]` of the execution order, x = W [x ; x0] + step[t], with x0 the embedding's
+    output, W [width, 2 width] and step [passes, width]."""
+    first_runs: Tuple[int, ...]
+    in_proj: str
+    step: str
+    hidden_size: int
+    kind: str = "loop_entry"
+
+    def tensors(self) -> TensorTable:
+        return {self.in_proj: ((self.hidden_size, 2 * self.hidden_size), "matrix"),
+                self.step: ((len(self.first_runs), self.hidden_size), "normal:0:0.02")}
+
+
+@dataclass(frozen=True)
 class LayerSpec:
     """One block: which parts and how they are arranged ('pre_norm': x += mixer(norm(x));
     x += ffn(norm(x)), the reference's order, runtime/src/text_model.cpp:146-168; 'parallel':
-    x += mixer(norm_a(x)) + ffn(norm_b(x)), both reading the stream as it enters)."""
+    x += mixer(norm_a(x)) + ffn(norm_b(x)), both reading the stream as it enters; a parallel block whose
+    ffn_norm is None while it has a feed-forward gives both parts the one normed input).
+    mixer_scale / ffn_scale name per-feature factors of the two parts' outputs ("layer scale") and
+    residual_mult multiplies what the block adds to the stream; the parallel block applies them."""
     mixer: object
     feed_forward: object
     mixer_norm: object
     ffn_norm: object
     block: str = "pre_norm"
+    mixer_scale: Optional[str] = None
+    ffn_scale: Optional[str] = None
+    residual_mult: float = 1.0
 
     def tensors(self) -> TensorTable:
         t: TensorTable = {}
         for part in (self.mixer_norm, self.mixer, self.ffn_norm, self.feed_forward):
             if part is not None:
                 t.update(part.tensors())
+        width = getattr(self.mixer_norm, "size", None)
+        for name in (self.mixer_scale, self.ffn_scale):
+            if name is not None:
+                t[name] = ((width,), "norm")
         return t
 
 
@@ -274,6 +402,7 @@ class ModelSpec:
     ignored_tensors: Tuple[str, ...] = ()     # name patterns (fnmatch) of stored buffers that are no weights
     max_position: int = 0
     logit_softcap: float = 0.0                # > 0: logits = cap * tanh(logits / cap)
+    loop: Optional[LoopSpec] = None           # where and how the stream re-enters a stretch of layers that runs again
 
     def __post_init__(self):
         if self.order is None:
@@ -290,6 +419,8 @@ class ModelSpec:
         for layer in self.layers:
             t.update(layer.tensors())
         t.update(self.final_norm.tensors())
+        if self.loop is not None:
+            t.update(self.loop.tensors())
         if self.lm_head is not None:
             t[self.lm_head] = ((self.vocab_size, self.hidden_size), "matrix")
         return t

@@ -29,8 +29,13 @@ def _generator(seed: int, name: str, device) -> torch.Generator:
 
 
 def draw_tensor(name: str, shape, kind: str, seed: int, device="cpu", dtype=torch.bfloat16) -> torch.Tensor:
-    """kind: 'matrix' -> N(0, 0.02); 'norm' -> 1 + N(0, 0.1); 'normal:<mean>:<std>'.  Drawn in float32, then rounded."""
+    """kind: 'matrix' -> N(0, 0.02); 'norm' -> 1 + N(0, 0.1); 'normal:<mean>:<std>'; 'choices:<count>' -> int32 rows of
+    distinct entries below count.  Floating tensors are drawn in float32, then rounded."""
     g = _generator(seed, name, torch.device(device))
+    if kind.startswith("choices:"):          # integer rows of distinct entries below the given count (a table of experts)
+        count = int(kind.split(":")[1])
+        keys = torch.rand((shape[0], count), generator=g, device=device)
+        return torch.argsort(keys, dim=1)[:, : shape[1]].to(torch.int32).contiguous()
     t = torch.randn(tuple(shape), generator=g, device=device, dtype=torch.float32)
     if kind == "norm":
         t = 1.0 + NORM_STD * t
