@@ -195,3 +195,354 @@ extern "C" int qv_diff_attention_generic(void* out, int ld_out, const void* q, i
   }
   return 0;
 }
+
+// ---------------------------------------------------------------- tensor cores (bfloat16)
+// qv_diff_attention_tc       a CTA serves a tile of 16 * MW query rows of one segment and one head with 2 * MW warps: warps
+//                            0..MW-1 run map 1 and warps MW..2MW-1 map 2, each over 16 rows; blocks of 64 keys (both maps' key
+//                            entries and the values) come through a two-stage cp.async ring that both maps read; Q.K^T and P.V as
+//                            mma.sync m16n8k16 with float32 sums, softmax in float32 (base 2); at the end map 2's warps leave
+//                            their normalised rows in shared memory and map 1's warps form a1 - lam * a2, the root mean square
+//                            over the head's values and the output.  Map and value sizes are padded with zeros up to the
+//                            template's (NT, DVT), so one instantiation serves all sizes below it (multiples of 8).
+//                            With `partial` (single query tokens whose keys are cut into slices, grid.x = slices) the two maps'
+//                            running maxima, sums and unnormalised rows go to a workspace that qv_diff_merge finishes.
+#define DIFF_KB 64
+
+__device__ __forceinline__ void dcp_async16(void* smem, const void* gmem, int bytes) {
+  const uint32_t s = (uint32_t)__cvta_generic_to_shared(smem);
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(s), "l"(gmem), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void dldsm4(uint32_t* r, const void* p) {
+  const uint32_t s = (uint32_t)__cvta_generic_to_shared(p);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
+}
+__device__ __forceinline__ void dldsm4t(uint32_t* r, const void* p) {
+  const uint32_t s = (uint32_t)__cvta_generic_to_shared(p);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
+}
+__device__ __forceinline__ void dmma(float* c, const uint32_t* a, uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t dpack(float lo, float hi) {
+  __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+  return *(uint32_t*)&h;
+}
+
+template <int NT, int DVT, int MW>
+__global__ void __launch_bounds__(64 * MW) diff_attention_tc_kernel(
+    bf16* __restrict__ out, int ld_out, const bf16* __restrict__ q, int ld_q, const bf16* __restrict__ cache,
+    const int* __restrict__ seg_q_start, const int* __restrict__ seg_pos0, const int* __restrict__ block_table, int max_blocks,
+    int H, int G, int n, int dv, int page, int window, float scale_log2, float lam, float eps, float post,
+    float* __restrict__ partial, int splits) {
+  constexpr int TM = 16 * MW, THREADS = 64 * MW;
+  constexpr int LDK = 2 * NT + 8, LDV = DVT + 8;          // padded rows: ldmatrix without bank conflicts
+  constexpr int STAGE = DIFF_KB * (LDK + LDV);            // elements of one stage (keys of both maps, then values)
+  extern __shared__ __align__(16) unsigned char diff_smem[];
+  bf16* Qs = (bf16*)diff_smem;                            // [TM][LDK]
+  bf16* ring = Qs + TM * LDK;                             // [2][STAGE]
+  pdl_wait();
+  pdl_launch_dependents();
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int mp = warp / MW, r0 = (warp % MW) * 16;        // this warp's map and first row of the tile
+  const int seg = blockIdx.y, h = blockIdx.z;
+  const int q0 = seg_q_start[seg], len = seg_q_start[seg + 1] - q0;
+  // single tokens in slices (partial): the tile is the token, blockIdx.x the slice; else blockIdx.x is the tile of rows
+  const int row0 = partial ? 0 : blockIdx.x * TM;
+  if (row0 >= len) return;
+  const int rows = len - row0 < TM ? len - row0 : TM;
+  const int pos0 = seg_pos0[seg] + row0;                  // position of the tile's first row
+  const int g = h / (H / G);
+  const size_t width = (size_t)G * (2 * n + dv);
+  const int* bt = block_table + (size_t)seg * max_blocks;
+  int kmin = window > 0 ? (pos0 - window + 1 > 0 ? pos0 - window + 1 : 0) : 0;
+  int kmax = pos0 + rows - 1;
+  int kb0 = (kmin / DIFF_KB) * DIFF_KB;
+  int nb = (kmax - kb0) / DIFF_KB + 1;
+  if (partial) {                                          // this slice's share of the blocks
+    const int per = (nb + splits - 1) / splits;
+    const int b_lo = blockIdx.x * per, b_hi = b_lo + per < nb ? b_lo + per : nb;
+    kb0 += b_lo * DIFF_KB;
+    nb = b_hi - b_lo;                                     // may be <= 0: an empty slice writes an empty partial
+  }
+
+  auto load_block = [&](int stage, int kb) {
+    bf16* Ks = ring + stage * STAGE;
+    bf16* Vs = Ks + DIFF_KB * LDK;
+    constexpr int KC = 2 * NT / 8, VC = DVT / 8;          // 16-byte pieces of a key row (both maps) and of a value row
+    for (int c = tid; c < DIFF_KB * (KC + VC); c += THREADS) {
+      const int j = c / (KC + VC), cc = c - j * (KC + VC);
+      const int key = kb + j;
+      const bool kin = key >= kmin && key <= kmax;
+      const bf16* row = cache;
+      if (kin) row = cache + ((size_t)bt[key / page] * page + (size_t)(key % page)) * width;
+      if (cc < KC) {
+        const int m = (cc * 8) / NT, within = cc * 8 - m * NT;
+        const bool ok = kin && within < n;
+        dcp_async16(Ks + j * LDK + cc * 8, ok ? row + (size_t)g * 2 * n + m * n + within : cache, ok ? 16 : 0);
+      } else {
+        const int col = (cc - KC) * 8;
+        const bool ok = kin && col < dv;
+        dcp_async16(Vs + j * LDV + col, ok ? row + (size_t)G * 2 * n + (size_t)g * dv + col : cache, ok ? 16 : 0);
+      }
+    }
+  };
+  {   // the tile's queries, both maps, zero-padded
+    constexpr int KC = 2 * NT / 8;
+    for (int c = tid; c < TM * KC; c += THREADS) {
+      const int r = c / KC, cc = c - r * KC;
+      const int m = (cc * 8) / NT, within = cc * 8 - m * NT;
+      const bool ok = r < rows && within < n;
+      dcp_async16(Qs + r * LDK + cc * 8, ok ? q + (size_t)(q0 + row0 + r) * ld_q + (size_t)h * 2 * n + m * n + within : q, ok ? 16 : 0);
+    }
+  }
+  if (nb > 0) load_block(0, kb0);
+  asm volatile("cp.async.commit_group;" ::: "memory");
+
+  const int gr = lane >> 2, tg = lane & 3;                // fragment row (and row + 8), column pair
+  int lo[2], hi[2];
+#pragma unroll
+  for (int e = 0; e < 2; ++e) {
+    const int r = r0 + gr + 8 * e;
+    const int p = pos0 + r;
+    hi[e] = r < rows ? p : -1;
+    lo[e] = window > 0 ? (p - window + 1 > 0 ? p - window + 1 : 0) : 0;
+  }
+  // keys any row of this warp can see
+  const int w_lo = window > 0 ? (pos0 + r0 - window + 1 > 0 ? pos0 + r0 - window + 1 : 0) : 0;
+  const int w_hi = r0 < rows ? pos0 + (r0 + 15 < rows - 1 ? r0 + 15 : rows - 1) : -1;
+  float o[DVT / 8][4];
+#pragma unroll
+  for (int i = 0; i < DVT / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+  float mrow[2] = {-INFINITY, -INFINITY}, lrow[2] = {0.f, 0.f};
+  uint32_t qf[NT / 16][4];
+
+  for (int b = 0; b < nb; ++b) {
+    if (b + 1 < nb) load_block((b + 1) & 1, kb0 + (b + 1) * DIFF_KB);
+    asm volatile("cp.async.commit_group;" ::: "memory");
+    asm volatile("cp.async.wait_group 1;" ::: "memory");
+    __syncthreads();
+    if (b == 0) {
+#pragma unroll
+      for (int kc = 0; kc < NT / 16; ++kc) dldsm4(qf[kc], Qs + (r0 + (lane & 15)) * LDK + mp * NT + kc * 16 + (lane >> 4) * 8);
+    }
+    const int kb = kb0 + b * DIFF_KB;
+    if (kb <= w_hi && kb + DIFF_KB - 1 >= w_lo) {
+      const bf16* Ks = ring + (b & 1) * STAGE;
+      const bf16* Vs = Ks + DIFF_KB * LDK;
+      float s[DIFF_KB / 8][4];
+#pragma unroll
+      for (int i = 0; i < DIFF_KB / 8; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
+#pragma unroll
+      for (int kc = 0; kc < NT / 16; ++kc) {
+#pragma unroll
+        for (int pr = 0; pr < DIFF_KB / 16; ++pr) {
+          uint32_t bfr[4];
+          dldsm4(bfr, Ks + (pr * 16 + (lane >> 4) * 8 + (lane & 7)) * LDK + mp * NT + kc * 16 + ((lane >> 3) & 1) * 8);
+          dmma(s[2 * pr], qf[kc], bfr[0], bfr[1]);
+          dmma(s[2 * pr + 1], qf[kc], bfr[2], bfr[3]);
+        }
+      }
+      float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+      for (int i = 0; i < DIFF_KB / 8; ++i) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int key = kb + i * 8 + 2 * tg + (e & 1), r = e >> 1;
+          const float v = (key >= lo[r] && key <= hi[r]) ? s[i][e] * scale_log2 : -INFINITY;
+          s[i][e] = v;
+          mx[r] = fmaxf(mx[r], v);
+        }
+      }
+      float corr[2];
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+        mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+        const float m_new = fmaxf(mrow[r], mx[r]);
+        corr[r] = (m_new == -INFINITY) ? 1.f : exp2f(mrow[r] - m_new);     // a row that has seen no key keeps -inf
+        mrow[r] = m_new;
+        lrow[r] *= corr[r];
+      }
+#pragma unroll
+      for (int i = 0; i < DIFF_KB / 8; ++i) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int r = e >> 1;
+          const float p = (s[i][e] == -INFINITY) ? 0.f : exp2f(s[i][e] - mrow[r]);
+          s[i][e] = p;
+          lrow[r] += p;
+        }
+      }
+#pragma unroll
+      for (int i = 0; i < DVT / 8; ++i) { o[i][0] *= corr[0]; o[i][1] *= corr[0]; o[i][2] *= corr[1]; o[i][3] *= corr[1]; }
+#pragma unroll
+      for (int kc = 0; kc < DIFF_KB / 16; ++kc) {
+        uint32_t a[4] = {dpack(s[2 * kc][0], s[2 * kc][1]), dpack(s[2 * kc][2], s[2 * kc][3]),
+                         dpack(s[2 * kc + 1][0], s[2 * kc + 1][1]), dpack(s[2 * kc + 1][2], s[2 * kc + 1][3])};
+#pragma unroll
+        for (int nt = 0; nt < DVT / 16; ++nt) {
+          uint32_t bfr[4];
+          dldsm4t(bfr, Vs + (kc * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * LDV + nt * 16 + (lane >> 4) * 8);
+          dmma(o[2 * nt], a, bfr[0], bfr[1]);
+          dmma(o[2 * nt + 1], a, bfr[2], bfr[3]);
+        }
+      }
+    }
+    __syncthreads();                         // the stage is free for the load after next
+  }
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    lrow[r] += __shfl_xor_sync(0xffffffffu, lrow[r], 1);
+    lrow[r] += __shfl_xor_sync(0xffffffffu, lrow[r], 2);
+  }
+  if (partial) {
+    // [token][head][slice][map][m, l, DVT values]: row 0 of the tile is the token
+    if (gr == 0 && r0 == 0) {
+      float* dst = partial + ((((size_t)seg * H + h) * splits + blockIdx.x) * 2 + mp) * (DVT + 2);
+      if (tg == 0) { dst[0] = mrow[0]; dst[1] = lrow[0]; }
+#pragma unroll
+      for (int i = 0; i < DVT / 8; ++i) { dst[2 + i * 8 + 2 * tg] = o[i][0]; dst[2 + i * 8 + 2 * tg + 1] = o[i][1]; }
+    }
+    return;
+  }
+  const float inv_l[2] = {lrow[0] > 0.f ? 1.0f / lrow[0] : 0.f, lrow[1] > 0.f ? 1.0f / lrow[1] : 0.f};
+  float* a2 = (float*)ring;                  // [TM][DVT + 1] float32, over the ring (all warps are past their last block)
+  constexpr int LDA = DVT + 1;
+  if (mp == 1) {
+#pragma unroll
+    for (int i = 0; i < DVT / 8; ++i) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) a2[(r0 + gr + 8 * (e >> 1)) * LDA + i * 8 + 2 * tg + (e & 1)] = o[i][e] * inv_l[e >> 1];
+    }
+  }
+  __syncthreads();
+  if (mp == 0) {
+    float ss[2] = {0.f, 0.f};
+#pragma unroll
+    for (int i = 0; i < DVT / 8; ++i) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float v = o[i][e] * inv_l[e >> 1] - lam * a2[(r0 + gr + 8 * (e >> 1)) * LDA + i * 8 + 2 * tg + (e & 1)];
+        o[i][e] = v;                         // columns from dv on are zero in both maps (their values were filled with zeros)
+        ss[e >> 1] = fmaf(v, v, ss[e >> 1]);
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      ss[r] += __shfl_xor_sync(0xffffffffu, ss[r], 1);
+      ss[r] += __shfl_xor_sync(0xffffffffu, ss[r], 2);
+      ss[r] = post / sqrtf(ss[r] / (float)dv + eps);
+    }
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      const int row = r0 + gr + 8 * r;
+      if (row >= rows) continue;
+      bf16* orow = out + (size_t)(q0 + row0 + row) * ld_out + (size_t)h * dv;
+#pragma unroll
+      for (int i = 0; i < DVT / 8; ++i) {
+        const int col = i * 8 + 2 * tg;
+        if (col < dv) *(__nv_bfloat162*)(orow + col) = __floats2bfloat162_rn(o[i][2 * r] * ss[r], o[i][2 * r + 1] * ss[r]);
+      }
+    }
+  }
+}
+
+// Finishes single tokens whose keys were cut into slices: per (token, head) the slices' maxima, sums and rows of both maps
+// are merged in the order of the slices, then o = a1 - lam * a2, the root mean square over dv, the output.  One warp each.
+template <int DVT>
+__global__ void __launch_bounds__(128) diff_merge_kernel(bf16* __restrict__ out, int ld_out, const float* __restrict__ partial, int T, int H,
+                                                         int dv, int splits, float lam, float eps, float post) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const int lane = threadIdx.x & 31;
+  const int idx = blockIdx.x * 4 + (threadIdx.x >> 5);
+  if (idx >= T * H) return;
+  const int t = idx / H, h = idx - t * H;
+  constexpr int NR = DVT / 32;
+  float a[2][NR];
+#pragma unroll
+  for (int mp = 0; mp < 2; ++mp) {
+    const float* base = partial + (((size_t)idx * splits) * 2 + mp) * (DVT + 2);
+    float m = -INFINITY;
+    for (int s = 0; s < splits; ++s) m = fmaxf(m, base[(size_t)s * 2 * (DVT + 2)]);
+    float l = 0.f;
+#pragma unroll
+    for (int r = 0; r < NR; ++r) a[mp][r] = 0.f;
+    for (int s = 0; s < splits; ++s) {
+      const float* p = base + (size_t)s * 2 * (DVT + 2);
+      const float w = p[0] == -INFINITY ? 0.f : exp2f(p[0] - m);
+      l = fmaf(w, p[1], l);
+#pragma unroll
+      for (int r = 0; r < NR; ++r) a[mp][r] = fmaf(w, p[2 + lane + 32 * r], a[mp][r]);
+    }
+    const float inv = l > 0.f ? 1.0f / l : 0.f;
+#pragma unroll
+    for (int r = 0; r < NR; ++r) a[mp][r] *= inv;
+  }
+  float ss = 0.f;
+#pragma unroll
+  for (int r = 0; r < NR; ++r) {
+    a[0][r] -= lam * a[1][r];
+    ss = fmaf(a[0][r], a[0][r], ss);
+  }
+  ss = warp_sum(ss);
+  const float k = post / sqrtf(ss / (float)dv + eps);
+  bf16* orow = out + (size_t)t * ld_out + (size_t)h * dv;
+#pragma unroll
+  for (int r = 0; r < NR; ++r) {
+    const int i = lane + 32 * r;
+    if (i < dv) orow[i] = __float2bfloat16_rn(a[0][r] * k);
+  }
+}
+
+static inline int diff_pad_n(int n) { return n <= 32 ? 32 : (n <= 64 ? 64 : 128); }
+static inline int diff_pad_dv(int dv) { return dv <= 64 ? 64 : (dv <= 128 ? 128 : 256); }
+
+// Floats of workspace per (token, head, slice) of single tokens whose keys are cut into slices.
+extern "C" long long qv_diff_partial_floats(int dv) { return 2LL * (diff_pad_dv(dv) + 2); }
+
+// S segments starting at rows seg_q_start[s] of q/out (and of the step), the longest of max_q_len rows.  splits > 1 (only
+// with max_q_len == 1): the keys of every token are cut into that many slices and `partial` (T * H * splits *
+// qv_diff_partial_floats floats) holds what the merge finishes.  Refuses (QV_ERR_UNSUPPORTED, nothing written) sizes it
+// does not take: map sizes above 128 or value sizes above 256, sizes that are no multiple of 8, rows that do not start
+// on 16 bytes.
+extern "C" int qv_diff_attention_tc(void* out, int ld_out, const void* q, int ld_q, const void* cache, const int* seg_q_start,
+                                    const int* seg_pos0, const int* block_table, int max_blocks, int S, int max_q_len, int H, int G, int n,
+                                    int dv, int page, int window, float scale, float lam, float eps, float post, float* partial, int splits,
+                                    void* stream) {
+  if (S <= 0 || max_q_len <= 0) return 0;
+  if (n <= 0 || n > 128 || (n & 7) || dv <= 0 || dv > 256 || (dv & 7) || G <= 0 || H % G || (ld_q & 7) || (ld_out & 1)) return QV_ERR_UNSUPPORTED;
+  if ((((uintptr_t)q | (uintptr_t)cache) & 15) || ((uintptr_t)out & 3) || ((G * (2 * n + dv)) & 7)) return QV_ERR_UNSUPPORTED;
+  if (splits > 1 && (max_q_len != 1 || !partial)) return QV_ERR_UNSUPPORTED;
+  if (S > 65535 || H > 65535) return QV_ERR_TOO_LARGE;
+  cudaStream_t st = (cudaStream_t)stream;
+  const int NT = diff_pad_n(n), DVT = diff_pad_dv(dv);
+  const bool small = max_q_len <= 16;
+  const int MW = small ? 1 : 4;
+  const size_t smem = (size_t)((16 * MW) * (2 * NT + 8) + 2 * DIFF_KB * (2 * NT + 8 + DVT + 8)) * sizeof(bf16);
+  const float scale_log2 = scale * 1.4426950408889634f;
+  float* part = splits > 1 ? partial : nullptr;
+  const dim3 grid(splits > 1 ? splits : (max_q_len + 16 * MW - 1) / (16 * MW), S, H);
+  int rc = QV_ERR_UNSUPPORTED;
+#define DIFF_LAUNCH(N_, DV_, MW_)                                                                                                   \
+  do {                                                                                                                              \
+    cudaFuncSetAttribute(diff_attention_tc_kernel<N_, DV_, MW_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);           \
+    rc = qv_launch(diff_attention_tc_kernel<N_, DV_, MW_>, grid, dim3(64 * MW_), smem, st, (bf16*)out, ld_out, (const bf16*)q, ld_q, \
+                   (const bf16*)cache, seg_q_start, seg_pos0, block_table, max_blocks, H, G, n, dv, page, window, scale_log2, lam, eps, \
+                   post, part, splits);                                                                                             \
+  } while (0)
+#define DIFF_BY_MW(N_, DV_) do { if (small) DIFF_LAUNCH(N_, DV_, 1); else DIFF_LAUNCH(N_, DV_, 4); } while (0)
+#define DIFF_BY_DV(N_) do { if (DVT == 64) DIFF_BY_MW(N_, 64); else if (DVT == 128) DIFF_BY_MW(N_, 128); else DIFF_BY_MW(N_, 256); } while (0)
+  if (NT == 32) DIFF_BY_DV(32); else if (NT == 64) DIFF_BY_DV(64); else DIFF_BY_DV(128);
+#undef DIFF_BY_DV
+#undef DIFF_BY_MW
+#undef DIFF_LAUNCH
+  if (rc || splits <= 1) return rc;
+  const int T = S;                                        // single tokens: a segment is a token
+  const dim3 mgrid((T * H + 3) / 4);
+  if (DVT == 64) return qv_launch(diff_merge_kernel<64>, mgrid, dim3(128), 0, st, (bf16*)out, ld_out, (const float*)partial, T, H, dv, splits, lam, eps, post);
+  if (DVT == 128) return qv_launch(diff_merge_kernel<128>, mgrid, dim3(128), 0, st, (bf16*)out, ld_out, (const float*)partial, T, H, dv, splits, lam, eps, post);
+  return qv_launch(diff_merge_kernel<256>, mgrid, dim3(128), 0, st, (bf16*)out, ld_out, (const float*)partial, T, H, dv, splits, lam, eps, post);
+}

@@ -79,12 +79,14 @@ _ARGTYPES = {
     "qv_add_vector": [_V, _V, _I, _I, _V],
     "qv_activation": [_V, _V, _L, _I, _I, _V],
     "qv_diff_prepare": [_V, _I, _V, _I, _V, _V, _V, _F, _V, _I, _V, _V, _V, _I, _V, _I, _I, _I, _I, _I, _I, _I, _I, _I, _V],
+    "qv_diff_partial_floats": [_I],
+    "qv_diff_attention_tc": [_V, _I, _V, _I, _V, _V, _V, _V, _I, _I, _I, _I, _I, _I, _I, _I, _I, _F, _F, _F, _F, _V, _I, _V],
     "qv_diff_attention_generic": [_V, _I, _V, _I, _V, _V, _V, _V, _I, _I, _I, _I, _I, _I, _I, _I, _F, _F, _F, _F, _I, _V],
     "qv_argmax": [_V, _V, _I, _I, _L, _V],
     "qv_sample": [_V, _V, _I, _I, _L, _V, _V, _V, _V, _V, _V, _I, _V, _V, _V, _V],
 }
 _RESTYPES = {"qv_error_string": ctypes.c_char_p, "qv_packed_weight_bytes": c_longlong, "qv_gemm_bf16_split_slot_bytes": c_longlong,
-             "qv_linear_scan_state_floats": c_longlong, "qv_latent_tc_workspace_bytes": c_longlong}
+             "qv_linear_scan_state_floats": c_longlong, "qv_latent_tc_workspace_bytes": c_longlong, "qv_diff_partial_floats": c_longlong}
 _typed_libs = {}
 
 
@@ -361,8 +363,60 @@ def diff_attention_generic(out, q, cache_layer, ctx, block_table, H, G, n, dv, p
     _check(rc, "diff_attention_generic")
 
 
+def diff_attention_tc(out, q, cache_layer, seg_q_start, seg_pos0, block_table, S, max_q_len, H, G, n, dv, page, window, scale, lam,
+                      eps, post, splits: int = 1) -> bool:
+    """Differential attention on the tensor cores (bfloat16; map sizes up to 128 and value sizes up to 256, multiples of 8)
+    for S segments that start at rows seg_q_start[s]; splits > 1 (single tokens only) cuts every token's keys into slices
+    that a second launch merges.  False, nothing written, for sizes it does not take."""
+    if q.dtype != torch.bfloat16 or n % 8 or dv % 8 or n > 128 or dv > 256 or q.stride(0) % 8:
+        return False
+    _need_cuda(out, q, cache_layer, seg_q_start, seg_pos0, block_table)
+    assert q.stride(1) == 1 and out.stride(1) == 1 and out.dtype == cache_layer.dtype == torch.bfloat16
+    assert cache_layer.is_contiguous() and tuple(cache_layer.shape[1:]) == (page, G * (2 * n + dv))
+    _i32(block_table, "block_table")
+    lib = _lib("diff_attention")
+    partial = None
+    if splits > 1:
+        assert max_q_len == 1
+        partial = torch.empty(S * H * splits * int(lib.qv_diff_partial_floats(dv)), device=q.device, dtype=torch.float32)
+    rc = lib.qv_diff_attention_tc(_ptr(out), out.stride(0), _ptr(q), q.stride(0), _ptr(cache_layer), _ptr(seg_q_start), _ptr(seg_pos0),
+                                  _ptr(block_table), block_table.shape[-1], S, max_q_len, H, G, n, dv, page, int(window), float(scale),
+                                  float(lam), float(eps), float(post), _ptr(partial), splits, _stream())
+    if rc == -2:
+        return False
+    _check(rc, "diff_attention_tc")
+    if splits > 1:
+        add_launches(1)                              # the merge of the slices
+    return True
+
+
+def diff_attention_splits(tokens: int, H: int, window: int, max_ctx: int) -> int:
+    """Into how many slices the keys of single query tokens are cut so that a step fills the SMs: a function of the
+    step's shape only (a captured step keeps it)."""
+    keys = min(window, max_ctx) if window > 0 else max_ctx
+    blocks = max(1, -(-keys // 64))
+    return max(1, min(2 * sm_count() // max(tokens * H, 1), blocks, 32))
+
+
 def diff_attention(out, q, cache_layer, ctx, block_table, H, G, n, dv, page, window, scale, lam, eps, post) -> None:
-    """Differential attention of every token of the step over its request's cache rows."""
+    """Differential attention of every token of the step over its request's cache rows.  bfloat16: the tensor-core
+    kernel where it takes the sizes (single tokens, which come first in a step, with tiles of 16 rows and their keys in
+    slices; portions with tiles of 64 rows); float32 and other sizes: the CUDA-core kernel."""
+    if q.dtype == torch.bfloat16:
+        S = ctx.num_segments
+        n1 = 0                                        # leading segments of one token (decoded tokens)
+        while n1 < S and ctx.seg_len[n1] == 1:
+            n1 += 1
+        args = (H, G, n, dv, page, window, scale, lam, eps, post)
+        ok = True
+        if n1:
+            splits = diff_attention_splits(n1, H, window, ctx.max_ctx_len)
+            ok = diff_attention_tc(out, q, cache_layer, ctx.seg_q_start, ctx.seg_pos0, block_table, n1, 1, *args, splits=splits)
+        if ok and n1 < S:
+            ok = diff_attention_tc(out, q, cache_layer, ctx.seg_q_start[n1:], ctx.seg_pos0[n1:], block_table[n1:], S - n1,
+                                   max(ctx.seg_len[n1:]), *args)
+        if ok:
+            return
     diff_attention_generic(out, q, cache_layer, ctx, block_table, H, G, n, dv, page, window, scale, lam, eps, post)
 
 

@@ -47,7 +47,7 @@ def _feed_forward_spec(f, p: str, width: int, vocab: int):
 
 def lotirax_spec(cfg: LotiraxConfig) -> ModelSpec:
     width, eps = cfg.width, cfg.norm_eps
-    layers = []
+    layers, optional = [], []
     for i, layer in enumerate(cfg.layers):
         p = f"l{i}."
         ff = _feed_forward_spec(layer.get("mlp"), p + "mlp.", width, cfg.vocab_size)
@@ -55,6 +55,8 @@ def lotirax_spec(cfg: LotiraxConfig) -> ModelSpec:
             mixer_norm=RMSNormSpec(width, eps, p + "norm1", one_plus=True), mixer=_mixer_spec(layer["type"], layer["mixer"], p + "mix.", width, eps),
             ffn_norm=None, feed_forward=ff, block="parallel", mixer_scale=p + "ls1", ffn_scale=p + "ls2" if ff is not None else None,
             residual_mult=cfg.residual_mult))
+        if ff is None:
+            optional.append(p + "ls2")           # a factor for a feed-forward the layer has not: passed over if stored
     runs = cfg.run_order()
     loop = None
     if cfg.loop is not None:
@@ -62,7 +64,8 @@ def lotirax_spec(cfg: LotiraxConfig) -> ModelSpec:
         first_runs = tuple(r for r, (i, t) in enumerate(runs) if t is not None and i == start)
         loop = LoopSpec(first_runs=first_runs, in_proj="loop.in", step="loop.step", hidden_size=width)
     return ModelSpec(architecture=cfg.architecture, vocab_size=cfg.vocab_size, hidden_size=width, embedding="embed", layers=layers,
-                     order=[i for i, _ in runs], final_norm=RMSNormSpec(width, eps, "final.norm", one_plus=True), lm_head=None, loop=loop)
+                     order=[i for i, _ in runs], final_norm=RMSNormSpec(width, eps, "final.norm", one_plus=True), lm_head=None, loop=loop,
+                     optional_tensors=tuple(optional))
 
 
 register_architecture("Lotirax", LotiraxConfig.from_dict, lotirax_spec)
