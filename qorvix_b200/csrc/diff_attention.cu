@@ -204,8 +204,9 @@ extern "C" int qv_diff_attention_generic(void* out, int ld_out, const void* q, i
 //                            their normalised rows in shared memory and map 1's warps form a1 - lam * a2, the root mean square
 //                            over the head's values and the output.  Map and value sizes are padded with zeros up to the
 //                            template's (NT, DVT), so one instantiation serves all sizes below it (multiples of 8).
-//                            With `partial` (single query tokens whose keys are cut into slices, grid.x = slices) the two maps'
-//                            running maxima, sums and unnormalised rows go to a workspace that qv_diff_merge finishes.
+//                            Single query tokens take a tile whose rows are the query heads of one key/value head (the keys are
+//                            read once for the group); their keys may be cut into slices (grid.x = slices): the two maps'
+//                            running maxima, sums and unnormalised rows then go to a workspace that the merge kernel finishes.
 #define DIFF_KB 64
 
 __device__ __forceinline__ void dcp_async16(void* smem, const void* gmem, int bytes) {
@@ -229,13 +230,16 @@ __device__ __forceinline__ uint32_t dpack(float lo, float hi) {
   return *(uint32_t*)&h;
 }
 
-template <int NT, int DVT, int MW>
-__global__ void __launch_bounds__(64 * MW) diff_attention_tc_kernel(
+template <int NT, int DVT, int MW, bool GROUPED>
+__global__ void __launch_bounds__(MW == 1 ? 128 : 64 * MW) diff_attention_tc_kernel(
     bf16* __restrict__ out, int ld_out, const bf16* __restrict__ q, int ld_q, const bf16* __restrict__ cache,
     const int* __restrict__ seg_q_start, const int* __restrict__ seg_pos0, const int* __restrict__ block_table, int max_blocks,
-    int H, int G, int n, int dv, int page, int window, float scale_log2, float lam, float eps, float post,
+    int H, int G, int n, int dv, int page, int page_shift, int window, float scale_log2, float lam, float eps, float post,
     float* __restrict__ partial, int splits) {
-  constexpr int TM = 16 * MW, THREADS = 64 * MW;
+  // GROUPED (single query tokens, MW == 1): the tile's rows are the query heads of one key/value head, which all see the
+  // same keys, so those are read once for the group; grid (slices, tokens, key/value heads).  Else the rows are tokens of
+  // one segment and one head; grid (tiles, segments, heads).  With MW == 1 two more warps only help to copy.
+  constexpr int TM = 16 * MW, THREADS = MW == 1 ? 128 : 64 * MW, NWARPS = THREADS / 32;
   constexpr int LDK = 2 * NT + 8, LDV = DVT + 8;          // padded rows: ldmatrix without bank conflicts
   constexpr int STAGE = DIFF_KB * (LDK + LDV);            // elements of one stage (keys of both maps, then values)
   extern __shared__ __align__(16) unsigned char diff_smem[];
@@ -244,56 +248,70 @@ __global__ void __launch_bounds__(64 * MW) diff_attention_tc_kernel(
   pdl_wait();
   pdl_launch_dependents();
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int mp = warp / MW, r0 = (warp % MW) * 16;        // this warp's map and first row of the tile
-  const int seg = blockIdx.y, h = blockIdx.z;
+  const bool computes = warp < 2 * MW;
+  const int mp = computes ? warp / MW : 0, r0 = (warp % MW) * 16;        // this warp's map and first row of the tile
+  const int seg = blockIdx.y;
+  const int hpg = H / G;
+  const int g = GROUPED ? blockIdx.z : blockIdx.z / hpg;
+  const int h = GROUPED ? g * hpg : blockIdx.z;           // the (first) head of the tile
   const int q0 = seg_q_start[seg], len = seg_q_start[seg + 1] - q0;
-  // single tokens in slices (partial): the tile is the token, blockIdx.x the slice; else blockIdx.x is the tile of rows
-  const int row0 = partial ? 0 : blockIdx.x * TM;
-  if (row0 >= len) return;
-  const int rows = len - row0 < TM ? len - row0 : TM;
+  const int row0 = GROUPED ? 0 : blockIdx.x * TM;
+  if (!GROUPED && row0 >= len) return;
+  const int rows = GROUPED ? hpg : (len - row0 < TM ? len - row0 : TM);
   const int pos0 = seg_pos0[seg] + row0;                  // position of the tile's first row
-  const int g = h / (H / G);
   const size_t width = (size_t)G * (2 * n + dv);
   const int* bt = block_table + (size_t)seg * max_blocks;
-  int kmin = window > 0 ? (pos0 - window + 1 > 0 ? pos0 - window + 1 : 0) : 0;
-  int kmax = pos0 + rows - 1;
+  const int kmin = window > 0 ? (pos0 - window + 1 > 0 ? pos0 - window + 1 : 0) : 0;
+  const int kmax = GROUPED ? pos0 : pos0 + rows - 1;
   int kb0 = (kmin / DIFF_KB) * DIFF_KB;
   int nb = (kmax - kb0) / DIFF_KB + 1;
-  if (partial) {                                          // this slice's share of the blocks
+  if (GROUPED && splits > 1) {                            // this slice's share of the blocks
     const int per = (nb + splits - 1) / splits;
     const int b_lo = blockIdx.x * per, b_hi = b_lo + per < nb ? b_lo + per : nb;
     kb0 += b_lo * DIFF_KB;
-    nb = b_hi - b_lo;                                     // may be <= 0: an empty slice writes an empty partial
+    nb = b_hi - b_lo;                                     // may be <= 0: an empty slice leaves an empty partial
   }
 
+  // a warp copies whole key rows: the row's place is worked out once, by all lanes alike, then every lane takes pieces
   auto load_block = [&](int stage, int kb) {
     bf16* Ks = ring + stage * STAGE;
     bf16* Vs = Ks + DIFF_KB * LDK;
     constexpr int KC = 2 * NT / 8, VC = DVT / 8;          // 16-byte pieces of a key row (both maps) and of a value row
-    for (int c = tid; c < DIFF_KB * (KC + VC); c += THREADS) {
-      const int j = c / (KC + VC), cc = c - j * (KC + VC);
+    for (int j = warp; j < DIFF_KB; j += NWARPS) {
       const int key = kb + j;
       const bool kin = key >= kmin && key <= kmax;
       const bf16* row = cache;
-      if (kin) row = cache + ((size_t)bt[key / page] * page + (size_t)(key % page)) * width;
-      if (cc < KC) {
-        const int m = (cc * 8) / NT, within = cc * 8 - m * NT;
-        const bool ok = kin && within < n;
-        dcp_async16(Ks + j * LDK + cc * 8, ok ? row + (size_t)g * 2 * n + m * n + within : cache, ok ? 16 : 0);
-      } else {
-        const int col = (cc - KC) * 8;
-        const bool ok = kin && col < dv;
-        dcp_async16(Vs + j * LDV + col, ok ? row + (size_t)G * 2 * n + (size_t)g * dv + col : cache, ok ? 16 : 0);
+      if (kin) {
+        const int pg = page_shift >= 0 ? key >> page_shift : key / page;
+        const int in_page = page_shift >= 0 ? key & (page - 1) : key - pg * page;
+        row = cache + ((size_t)bt[pg] * page + (size_t)in_page) * width;
+      }
+      const bf16* krow = row + (size_t)g * 2 * n;
+      const bf16* vrow = row + (size_t)G * 2 * n + (size_t)g * dv;
+#pragma unroll
+      for (int cc = lane; cc < KC + VC; cc += 32) {
+        if (cc < KC) {
+          const int m = (cc * 8) / NT, within = cc * 8 - m * NT;
+          const bool ok = kin && within < n;
+          dcp_async16(Ks + j * LDK + cc * 8, ok ? krow + m * n + within : cache, ok ? 16 : 0);
+        } else {
+          const int col = (cc - KC) * 8;
+          const bool ok = kin && col < dv;
+          dcp_async16(Vs + j * LDV + col, ok ? vrow + col : cache, ok ? 16 : 0);
+        }
       }
     }
   };
   {   // the tile's queries, both maps, zero-padded
     constexpr int KC = 2 * NT / 8;
-    for (int c = tid; c < TM * KC; c += THREADS) {
-      const int r = c / KC, cc = c - r * KC;
-      const int m = (cc * 8) / NT, within = cc * 8 - m * NT;
-      const bool ok = r < rows && within < n;
-      dcp_async16(Qs + r * LDK + cc * 8, ok ? q + (size_t)(q0 + row0 + r) * ld_q + (size_t)h * 2 * n + m * n + within : q, ok ? 16 : 0);
+    for (int r = warp; r < TM; r += NWARPS) {
+      const bf16* qrow = GROUPED ? q + (size_t)q0 * ld_q + (size_t)(h + r) * 2 * n : q + (size_t)(q0 + row0 + r) * ld_q + (size_t)h * 2 * n;
+#pragma unroll
+      for (int cc = lane; cc < KC; cc += 32) {
+        const int m = (cc * 8) / NT, within = cc * 8 - m * NT;
+        const bool ok = r < rows && within < n;
+        dcp_async16(Qs + r * LDK + cc * 8, ok ? qrow + m * n + within : q, ok ? 16 : 0);
+      }
     }
   }
   if (nb > 0) load_block(0, kb0);
@@ -304,13 +322,16 @@ __global__ void __launch_bounds__(64 * MW) diff_attention_tc_kernel(
 #pragma unroll
   for (int e = 0; e < 2; ++e) {
     const int r = r0 + gr + 8 * e;
-    const int p = pos0 + r;
+    const int p = GROUPED ? pos0 : pos0 + r;
     hi[e] = r < rows ? p : -1;
     lo[e] = window > 0 ? (p - window + 1 > 0 ? p - window + 1 : 0) : 0;
   }
-  // keys any row of this warp can see
-  const int w_lo = window > 0 ? (pos0 + r0 - window + 1 > 0 ? pos0 + r0 - window + 1 : 0) : 0;
-  const int w_hi = r0 < rows ? pos0 + (r0 + 15 < rows - 1 ? r0 + 15 : rows - 1) : -1;
+  // keys any row of this warp can see, and keys all of its rows see
+  const int p_first = GROUPED ? pos0 : pos0 + r0, p_last = GROUPED ? pos0 : pos0 + (r0 + 15 < rows - 1 ? r0 + 15 : rows - 1);
+  const int w_lo = window > 0 ? (p_first - window + 1 > 0 ? p_first - window + 1 : 0) : 0;
+  const int w_hi = r0 < rows ? p_last : -1;
+  const int all_lo = window > 0 ? (p_last - window + 1 > 0 ? p_last - window + 1 : 0) : 0;
+  const int all_hi = (r0 + 15 < rows) ? p_first : -1;     // a tile with rows past its end masks them in every block
   float o[DVT / 8][4];
 #pragma unroll
   for (int i = 0; i < DVT / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
@@ -322,12 +343,12 @@ __global__ void __launch_bounds__(64 * MW) diff_attention_tc_kernel(
     asm volatile("cp.async.commit_group;" ::: "memory");
     asm volatile("cp.async.wait_group 1;" ::: "memory");
     __syncthreads();
-    if (b == 0) {
+    if (b == 0 && computes) {
 #pragma unroll
       for (int kc = 0; kc < NT / 16; ++kc) dldsm4(qf[kc], Qs + (r0 + (lane & 15)) * LDK + mp * NT + kc * 16 + (lane >> 4) * 8);
     }
     const int kb = kb0 + b * DIFF_KB;
-    if (kb <= w_hi && kb + DIFF_KB - 1 >= w_lo) {
+    if (computes && kb <= w_hi && kb + DIFF_KB - 1 >= w_lo) {
       const bf16* Ks = ring + (b & 1) * STAGE;
       const bf16* Vs = Ks + DIFF_KB * LDK;
       float s[DIFF_KB / 8][4];
@@ -344,14 +365,25 @@ __global__ void __launch_bounds__(64 * MW) diff_attention_tc_kernel(
         }
       }
       float mx[2] = {-INFINITY, -INFINITY};
+      if (kb >= all_lo && kb + DIFF_KB - 1 <= all_hi) {   // every row of the warp sees the whole block: nothing to mask
 #pragma unroll
-      for (int i = 0; i < DIFF_KB / 8; ++i) {
+        for (int i = 0; i < DIFF_KB / 8; ++i) {
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const int key = kb + i * 8 + 2 * tg + (e & 1), r = e >> 1;
-          const float v = (key >= lo[r] && key <= hi[r]) ? s[i][e] * scale_log2 : -INFINITY;
-          s[i][e] = v;
-          mx[r] = fmaxf(mx[r], v);
+          for (int e = 0; e < 4; ++e) {
+            s[i][e] *= scale_log2;
+            mx[e >> 1] = fmaxf(mx[e >> 1], s[i][e]);
+          }
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < DIFF_KB / 8; ++i) {
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int key = kb + i * 8 + 2 * tg + (e & 1), r = e >> 1;
+            const float v = (key >= lo[r] && key <= hi[r]) ? s[i][e] * scale_log2 : -INFINITY;
+            s[i][e] = v;
+            mx[r] = fmaxf(mx[r], v);
+          }
         }
       }
       float corr[2];
@@ -364,12 +396,13 @@ __global__ void __launch_bounds__(64 * MW) diff_attention_tc_kernel(
         mrow[r] = m_new;
         lrow[r] *= corr[r];
       }
+      const float mref[2] = {mrow[0] == -INFINITY ? 0.f : mrow[0], mrow[1] == -INFINITY ? 0.f : mrow[1]};
 #pragma unroll
       for (int i = 0; i < DIFF_KB / 8; ++i) {
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
           const int r = e >> 1;
-          const float p = (s[i][e] == -INFINITY) ? 0.f : exp2f(s[i][e] - mrow[r]);
+          const float p = exp2f(s[i][e] - mref[r]);       // a masked score is -inf: its weight is 0
           s[i][e] = p;
           lrow[r] += p;
         }
@@ -397,20 +430,25 @@ __global__ void __launch_bounds__(64 * MW) diff_attention_tc_kernel(
     lrow[r] += __shfl_xor_sync(0xffffffffu, lrow[r], 1);
     lrow[r] += __shfl_xor_sync(0xffffffffu, lrow[r], 2);
   }
-  if (partial) {
-    // [token][head][slice][map][m, l, DVT values]: row 0 of the tile is the token
-    if (gr == 0 && r0 == 0) {
-      float* dst = partial + ((((size_t)seg * H + h) * splits + blockIdx.x) * 2 + mp) * (DVT + 2);
-      if (tg == 0) { dst[0] = mrow[0]; dst[1] = lrow[0]; }
+  if (GROUPED && splits > 1) {
+    // [token][head][slice][map][m, l, DVT values]; the tile's rows are the group's heads
+    if (computes) {
 #pragma unroll
-      for (int i = 0; i < DVT / 8; ++i) { dst[2 + i * 8 + 2 * tg] = o[i][0]; dst[2 + i * 8 + 2 * tg + 1] = o[i][1]; }
+      for (int e = 0; e < 2; ++e) {
+        const int row = gr + 8 * e;
+        if (row >= rows) continue;
+        float* dst = partial + ((((size_t)seg * H + h + row) * splits + blockIdx.x) * 2 + mp) * (DVT + 2);
+        if (tg == 0) { dst[0] = mrow[e]; dst[1] = lrow[e]; }
+#pragma unroll
+        for (int i = 0; i < DVT / 8; ++i) { dst[2 + i * 8 + 2 * tg] = o[i][2 * e]; dst[2 + i * 8 + 2 * tg + 1] = o[i][2 * e + 1]; }
+      }
     }
     return;
   }
   const float inv_l[2] = {lrow[0] > 0.f ? 1.0f / lrow[0] : 0.f, lrow[1] > 0.f ? 1.0f / lrow[1] : 0.f};
   float* a2 = (float*)ring;                  // [TM][DVT + 1] float32, over the ring (all warps are past their last block)
   constexpr int LDA = DVT + 1;
-  if (mp == 1) {
+  if (computes && mp == 1) {
 #pragma unroll
     for (int i = 0; i < DVT / 8; ++i) {
 #pragma unroll
@@ -418,7 +456,7 @@ __global__ void __launch_bounds__(64 * MW) diff_attention_tc_kernel(
     }
   }
   __syncthreads();
-  if (mp == 0) {
+  if (computes && mp == 0) {
     float ss[2] = {0.f, 0.f};
 #pragma unroll
     for (int i = 0; i < DVT / 8; ++i) {
@@ -439,7 +477,7 @@ __global__ void __launch_bounds__(64 * MW) diff_attention_tc_kernel(
     for (int r = 0; r < 2; ++r) {
       const int row = r0 + gr + 8 * r;
       if (row >= rows) continue;
-      bf16* orow = out + (size_t)(q0 + row0 + row) * ld_out + (size_t)h * dv;
+      bf16* orow = GROUPED ? out + (size_t)q0 * ld_out + (size_t)(h + row) * dv : out + (size_t)(q0 + row0 + row) * ld_out + (size_t)h * dv;
 #pragma unroll
       for (int i = 0; i < DVT / 8; ++i) {
         const int col = i * 8 + 2 * tg;
@@ -503,19 +541,20 @@ static inline int diff_pad_dv(int dv) { return dv <= 64 ? 64 : (dv <= 128 ? 128 
 // Floats of workspace per (token, head, slice) of single tokens whose keys are cut into slices.
 extern "C" long long qv_diff_partial_floats(int dv) { return 2LL * (diff_pad_dv(dv) + 2); }
 
-// S segments starting at rows seg_q_start[s] of q/out (and of the step), the longest of max_q_len rows.  splits > 1 (only
-// with max_q_len == 1): the keys of every token are cut into that many slices and `partial` (T * H * splits *
-// qv_diff_partial_floats floats) holds what the merge finishes.  Refuses (QV_ERR_UNSUPPORTED, nothing written) sizes it
-// does not take: map sizes above 128 or value sizes above 256, sizes that are no multiple of 8, rows that do not start
-// on 16 bytes.
+// S segments starting at rows seg_q_start[s] of q/out (and of the step), the longest of max_q_len rows.  With max_q_len == 1
+// and at most 16 query heads per key/value head the heads of a group share a tile (the keys are read once for them) and
+// splits > 1 cuts every token's keys into that many slices: `partial` (S * H * splits * qv_diff_partial_floats floats) then
+// holds what the merge finishes.  Refuses (QV_ERR_UNSUPPORTED, nothing written) sizes it does not take: map sizes above
+// 128 or value sizes above 256, sizes that are no multiple of 8, rows that do not start on 16 bytes.
 extern "C" int qv_diff_attention_tc(void* out, int ld_out, const void* q, int ld_q, const void* cache, const int* seg_q_start,
                                     const int* seg_pos0, const int* block_table, int max_blocks, int S, int max_q_len, int H, int G, int n,
                                     int dv, int page, int window, float scale, float lam, float eps, float post, float* partial, int splits,
                                     void* stream) {
   if (S <= 0 || max_q_len <= 0) return 0;
-  if (n <= 0 || n > 128 || (n & 7) || dv <= 0 || dv > 256 || (dv & 7) || G <= 0 || H % G || (ld_q & 7) || (ld_out & 1)) return QV_ERR_UNSUPPORTED;
+  if (n <= 0 || n > 128 || (n & 7) || dv <= 0 || dv > 256 || (dv & 7) || G <= 0 || H % G || (ld_q & 7) || (ld_out & 1) || page <= 0) return QV_ERR_UNSUPPORTED;
   if ((((uintptr_t)q | (uintptr_t)cache) & 15) || ((uintptr_t)out & 3) || ((G * (2 * n + dv)) & 7)) return QV_ERR_UNSUPPORTED;
-  if (splits > 1 && (max_q_len != 1 || !partial)) return QV_ERR_UNSUPPORTED;
+  const bool grouped = max_q_len == 1 && H / G <= 16;
+  if (splits > 1 && (!grouped || !partial)) return QV_ERR_UNSUPPORTED;
   if (S > 65535 || H > 65535) return QV_ERR_TOO_LARGE;
   cudaStream_t st = (cudaStream_t)stream;
   const int NT = diff_pad_n(n), DVT = diff_pad_dv(dv);
@@ -523,17 +562,24 @@ extern "C" int qv_diff_attention_tc(void* out, int ld_out, const void* q, int ld
   const int MW = small ? 1 : 4;
   const size_t smem = (size_t)((16 * MW) * (2 * NT + 8) + 2 * DIFF_KB * (2 * NT + 8 + DVT + 8)) * sizeof(bf16);
   const float scale_log2 = scale * 1.4426950408889634f;
-  float* part = splits > 1 ? partial : nullptr;
-  const dim3 grid(splits > 1 ? splits : (max_q_len + 16 * MW - 1) / (16 * MW), S, H);
+  int page_shift = -1;
+  if ((page & (page - 1)) == 0) for (page_shift = 0; (1 << page_shift) < page; ++page_shift) {}
+  if (splits < 1) splits = 1;
+  const dim3 grid(grouped ? splits : (max_q_len + 16 * MW - 1) / (16 * MW), S, grouped ? G : H);
   int rc = QV_ERR_UNSUPPORTED;
-#define DIFF_LAUNCH(N_, DV_, MW_)                                                                                                   \
+#define DIFF_LAUNCH(N_, DV_, MW_, GR_)                                                                                              \
   do {                                                                                                                              \
-    cudaFuncSetAttribute(diff_attention_tc_kernel<N_, DV_, MW_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);           \
-    rc = qv_launch(diff_attention_tc_kernel<N_, DV_, MW_>, grid, dim3(64 * MW_), smem, st, (bf16*)out, ld_out, (const bf16*)q, ld_q, \
-                   (const bf16*)cache, seg_q_start, seg_pos0, block_table, max_blocks, H, G, n, dv, page, window, scale_log2, lam, eps, \
-                   post, part, splits);                                                                                             \
+    cudaFuncSetAttribute(diff_attention_tc_kernel<N_, DV_, MW_, GR_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);      \
+    rc = qv_launch(diff_attention_tc_kernel<N_, DV_, MW_, GR_>, grid, dim3(MW_ == 1 ? 128 : 64 * MW_), smem, st, (bf16*)out, ld_out, \
+                   (const bf16*)q, ld_q, (const bf16*)cache, seg_q_start, seg_pos0, block_table, max_blocks, H, G, n, dv, page,     \
+                   page_shift, window, scale_log2, lam, eps, post, partial, splits);                                                \
   } while (0)
-#define DIFF_BY_MW(N_, DV_) do { if (small) DIFF_LAUNCH(N_, DV_, 1); else DIFF_LAUNCH(N_, DV_, 4); } while (0)
+#define DIFF_BY_MW(N_, DV_)                                                   \
+  do {                                                                        \
+    if (grouped) DIFF_LAUNCH(N_, DV_, 1, true);                               \
+    else if (small) DIFF_LAUNCH(N_, DV_, 1, false);                           \
+    else DIFF_LAUNCH(N_, DV_, 4, false);                                      \
+  } while (0)
 #define DIFF_BY_DV(N_) do { if (DVT == 64) DIFF_BY_MW(N_, 64); else if (DVT == 128) DIFF_BY_MW(N_, 128); else DIFF_BY_MW(N_, 256); } while (0)
   if (NT == 32) DIFF_BY_DV(32); else if (NT == 64) DIFF_BY_DV(64); else DIFF_BY_DV(128);
 #undef DIFF_BY_DV

@@ -366,8 +366,8 @@ def diff_attention_generic(out, q, cache_layer, ctx, block_table, H, G, n, dv, p
 def diff_attention_tc(out, q, cache_layer, seg_q_start, seg_pos0, block_table, S, max_q_len, H, G, n, dv, page, window, scale, lam,
                       eps, post, splits: int = 1) -> bool:
     """Differential attention on the tensor cores (bfloat16; map sizes up to 128 and value sizes up to 256, multiples of 8)
-    for S segments that start at rows seg_q_start[s]; splits > 1 (single tokens only) cuts every token's keys into slices
-    that a second launch merges.  False, nothing written, for sizes it does not take."""
+    for S segments that start at rows seg_q_start[s]; single tokens share a tile among the query heads of a key/value
+    head, and splits > 1 (single tokens only) cuts every token's keys into slices that a second launch merges.  False, nothing written, for sizes it does not take."""
     if q.dtype != torch.bfloat16 or n % 8 or dv % 8 or n > 128 or dv > 256 or q.stride(0) % 8:
         return False
     _need_cuda(out, q, cache_layer, seg_q_start, seg_pos0, block_table)
@@ -390,12 +390,15 @@ def diff_attention_tc(out, q, cache_layer, seg_q_start, seg_pos0, block_table, S
     return True
 
 
-def diff_attention_splits(tokens: int, H: int, window: int, max_ctx: int) -> int:
-    """Into how many slices the keys of single query tokens are cut so that a step fills the SMs: a function of the
-    step's shape only (a captured step keeps it)."""
+def diff_attention_splits(tokens: int, H: int, G: int, window: int, max_ctx: int) -> int:
+    """Into how many slices the keys of single query tokens are cut so that a step fills the SMs (a CTA serves a token
+    and a key/value head): a function of the step's shape only (a captured step keeps it).  One, where a key/value
+    head has more than 16 query heads (those do not share a tile)."""
+    if H // G > 16:
+        return 1
     keys = min(window, max_ctx) if window > 0 else max_ctx
     blocks = max(1, -(-keys // 64))
-    return max(1, min(2 * sm_count() // max(tokens * H, 1), blocks, 32))
+    return max(1, min(2 * sm_count() // max(tokens * G, 1), blocks, 32))
 
 
 def diff_attention(out, q, cache_layer, ctx, block_table, H, G, n, dv, page, window, scale, lam, eps, post) -> None:
@@ -410,7 +413,7 @@ def diff_attention(out, q, cache_layer, ctx, block_table, H, G, n, dv, page, win
         args = (H, G, n, dv, page, window, scale, lam, eps, post)
         ok = True
         if n1:
-            splits = diff_attention_splits(n1, H, window, ctx.max_ctx_len)
+            splits = diff_attention_splits(n1, H, G, window, ctx.max_ctx_len)
             ok = diff_attention_tc(out, q, cache_layer, ctx.seg_q_start, ctx.seg_pos0, block_table, n1, 1, *args, splits=splits)
         if ok and n1 < S:
             ok = diff_attention_tc(out, q, cache_layer, ctx.seg_q_start[n1:], ctx.seg_pos0[n1:], block_table[n1:], S - n1,

@@ -1,9 +1,9 @@
-"""Prefill and decode throughput of a Deganex model at layer sizes that resemble real models, beside the Llama
-decoder at equal width, depth and active feed-forward size, and the Deganex kernels alone with their roofline
+"""Prefill and decode throughput of a Deganex or a Lotirax model at layer sizes that resemble real models, beside the
+Llama decoder at equal width, depth and (active) feed-forward size, and the design's kernels alone with their roofline
 fractions beside the Llama kernels they correspond to.
 
-    python bench.py --design deganex [--layers-per-kind 2] [--batch 8] [--ctx 1024] [--prefill-tokens 2048]
-    python -m qorvix_b200.design_bench
+    python bench.py --design deganex|lotirax [--layers-per-kind 2] [--batch 8] [--ctx 1024] [--prefill-tokens 2048]
+    python -m qorvix_b200.design_bench [--design lotirax]
 
 Random bfloat16 weights; timing with CUDA events after warm-up; kernels alone are timed in captured chains over
 buffers larger than L2 (kernel_bench.timed_chain).  Figures go out as one JSON line.
@@ -198,6 +198,126 @@ def experts_case(T, peaks) -> dict:
     return kb._figures(us, nbytes, 2.0 * R * 3 * ff * d, peaks)
 
 
+# ---------------------------------------------------------------------------------------------- Lotirax
+# Sixteen heads of two 64-wide maps over 128 values, four key/value heads, a window of 1,024 keys, rotation over the
+# whole map with stretching; dense feed-forwards of 8,192 alternate with 64 small experts of 1,024 of which 4 serve a
+# token beside a shared one of 2,048; the two middle layers run twice.
+LOT_ATTN = {"heads": 16, "kv_heads": 4, "dim": 64, "vdim": 128, "scale": 0.125, "diff": 0.3, "mask": {"size": 1024},
+            "rot": {"base": 250000.0, "dims": 64, "scaling": {"factor": 4.0, "original": 2048, "fast": 32.0, "slow": 1.0}}}
+LOT_DENSE = {"kind": "dense", "ff": 8192}
+LOT_MOE = {"kind": "moe", "expert": {"ff": 1024}, "router": {"experts": 64, "top": 4}, "shared": {"ff": 2048}}
+
+
+def lotirax_config() -> dict:
+    layers = [{"type": "attention", "mixer": LOT_ATTN, "mlp": f} for f in (LOT_DENSE, LOT_MOE, LOT_DENSE, LOT_MOE)]
+    return {"architecture": "Lotirax", "vocab": VOCAB, "width": WIDTH, "norm": {"eps": 1e-5}, "residual_mult": 0.3, "layers": layers,
+            "loop": {"start": 1, "stop": 3, "times": 2}}
+
+
+def lotirax_llama_config(n_layers: int) -> dict:
+    return {"architectures": ["LlamaForCausalLM"], "vocab_size": VOCAB, "hidden_size": WIDTH, "intermediate_size": LOT_DENSE["ff"],
+            "num_hidden_layers": n_layers, "num_attention_heads": LOT_ATTN["heads"], "num_key_value_heads": LOT_ATTN["kv_heads"],
+            "head_dim": 128, "max_position_embeddings": 8192, "rms_norm_eps": 1e-5, "rope_theta": 10000.0, "tie_word_embeddings": True}
+
+
+def diff_attention_case(seg_lens, ctx_len, peaks, page=16) -> dict:
+    """Differential attention of the given segments, each ending at ctx_len cached tokens (the preparing kernel excluded)."""
+    a = LOT_ATTN
+    H, G, n, dv, W = a["heads"], a["kv_heads"], a["dim"], a["vdim"], a["mask"]["size"]
+    S, T = len(seg_lens), sum(seg_lens)
+    blocks = -(-ctx_len // page)
+    width = G * (2 * n + dv)
+    copies = max(2, min(8, int(2.5 * kb.L2_BYTES // (S * min(ctx_len, W + max(seg_lens)) * width * 2)) + 1))
+    caches = torch.randn(copies, S * blocks + 1, page, width, device="cuda", dtype=torch.bfloat16)
+    table = torch.arange(S * blocks, dtype=torch.int32, device="cuda").view(S, blocks)
+    ctx = _ctx(seg_lens, [ctx_len - m for m in seg_lens])
+    ctx.seg_len, ctx.seg_start_pos, ctx.max_ctx_len, ctx.captured = list(seg_lens), [ctx_len - m for m in seg_lens], ctx_len, False
+    ctx.seg_pos0 = torch.tensor(ctx.seg_start_pos, dtype=torch.int32, device="cuda")
+    q = torch.randn(T, H * 2 * n, device="cuda", dtype=torch.bfloat16)
+    out = torch.empty(T, H * dv, device="cuda", dtype=torch.bfloat16)
+    us = kb.timed_chain(lambda i: ops.diff_attention(out, q, caches[i % copies], ctx, table, H, G, n, dv, page, W, a["scale"], 0.4, 1e-5, 0.7),
+                        launches=8)
+    pairs = sum(sum(min(p + 1, W) for p in range(ctx_len - m, ctx_len)) for m in seg_lens)      # (query, key) pairs per head
+    keys_read = sum(min(ctx_len, W + m - 1) for m in seg_lens)
+    flops = H * pairs * (4.0 * n + 4.0 * dv)
+    return kb._figures(us, keys_read * width * 2 + (q.numel() + out.numel()) * 2, flops, peaks)
+
+
+def diff_prepare_case(T, peaks, page=16) -> dict:
+    """Bias, per-map norm, rotation and cache write of T tokens of one request."""
+    from .parts.rotary import inverse_frequencies
+    a = LOT_ATTN
+    H, G, n, dv = a["heads"], a["kv_heads"], a["dim"], a["vdim"]
+    cols, width = (H + G) * 2 * n + G * dv, G * (2 * n + dv)
+    copies = max(2, min(8, int(2.5 * kb.L2_BYTES // (T * (cols * 4 + width * 2 + H * 2 * n * 2))) + 1))
+    projs = torch.randn(copies, T, cols, device="cuda", dtype=torch.float32)
+    blocks = -(-T // page)
+    caches = torch.zeros(copies, blocks + 1, page, width, device="cuda", dtype=torch.bfloat16)
+    table = torch.arange(blocks, dtype=torch.int32, device="cuda").view(1, blocks)
+    ctx = _ctx([T], [0])
+    ang = torch.arange(T, dtype=torch.float64)[:, None] * inverse_frequencies(n, a["rot"]["base"])[None, :]
+    cos_sin = torch.stack([torch.cos(ang), torch.sin(ang)], dim=-1).float().cuda().contiguous()
+    bias = torch.randn(cols, device="cuda")
+    w = torch.ones(n, device="cuda")
+    q = torch.empty(copies, T, H * 2 * n, device="cuda", dtype=torch.bfloat16)
+    us = kb.timed_chain(lambda i: ops.diff_prepare(q[i % copies], projs[i % copies], bias, w, w, 1e-5, cos_sin, ctx, table, caches[i % copies],
+                                                   H, G, n, dv, n, page), launches=8)
+    return kb._figures(us, T * (cols * 4 + width * 2 + H * 2 * n * 2), 0.0, peaks)
+
+
+def table_experts_case(T, peaks) -> dict:
+    """Both products of the table-routed ungated experts for T tokens (look-up and grouping included, shared expert excluded)."""
+    E, top, ff, d = LOT_MOE["router"]["experts"], LOT_MOE["router"]["top"], LOT_MOE["expert"]["ff"], WIDTH
+    wbytes = E * 2 * ff * d * 2
+    copies = max(2, int(2.5 * kb.L2_BYTES // wbytes) + 1)
+    wu = [ops.moe_pack_experts(torch.randn(E, ff, d, device="cuda", dtype=torch.bfloat16) * 0.02) for _ in range(copies)]
+    wd = [ops.moe_pack_experts(torch.randn(E, d, ff, device="cuda", dtype=torch.bfloat16) * 0.02) for _ in range(copies)]
+    table = torch.argsort(torch.rand(VOCAB, E, device="cuda"), dim=1)[:, :top].to(torch.int32).contiguous()
+    ids = torch.randint(0, VOCAB, (T,), device="cuda", dtype=torch.int32)
+    x = torch.randn(T, d, device="cuda", dtype=torch.bfloat16)
+    R = T * top
+    top_idx = torch.empty(T, top, device="cuda", dtype=torch.int32)
+    top_w = torch.empty(T, top, device="cuda", dtype=torch.float32)
+    tile_rows = ops.moe_tile_rows(True)
+    ints = torch.empty(3 * R + 3 * ops.moe_max_tiles(R, E, tile_rows), device="cuda", dtype=torch.int32)
+    row_token, slot_row, scratch, tiles = ints[:R], ints[R:2 * R], ints[2 * R:3 * R], ints[3 * R:]
+    act = torch.empty(R, ff, device="cuda", dtype=torch.bfloat16)
+    y = torch.empty(R, d, device="cuda", dtype=torch.float32)
+    delta = torch.empty(T, d, device="cuda", dtype=torch.float32)
+    scale = torch.ones(d, device="cuda")
+
+    def run(i):
+        ops.moe_route_table(top_idx, top_w, table, ids, E)
+        ops.moe_group(row_token, slot_row, tiles, top_idx, scratch, E, tile_rows)
+        ops.moe_experts_tc(2, act, x, wu[i % copies], None, row_token, tiles)
+        ops.moe_experts_tc(0, y, act, wd[i % copies], None, row_token, tiles)
+        ops.moe_combine(delta, None, y, slot_row, top_w, None, None, ff_scale=scale)
+
+    us = kb.timed_chain(run, launches=6)
+    touched = min(E, R)
+    nbytes = touched * 2 * ff * d * 2 + T * d * 2 + R * (ff * 2 * 2 + d * 4 * 2) + T * d * 4
+    return kb._figures(us, nbytes, 2.0 * R * 2 * ff * d, peaks)
+
+
+def run_lotirax(args, peaks) -> dict:
+    raw = lotirax_config()
+    n_runs = 6
+    res = {"lotirax": model_throughput(raw, args.batch, args.ctx, args.prefill_tokens, args.steps, args.warmup),
+           "llama_equal_size": model_throughput(lotirax_llama_config(n_runs), args.batch, args.ctx, args.prefill_tokens, args.steps, args.warmup)}
+    T, B, C = args.prefill_tokens, args.batch, args.ctx
+    res["kernels"] = {
+        f"diff_attention_prefill_t{T}": diff_attention_case([T], T, peaks),
+        f"diff_attention_decode_b{B}_ctx{C}": diff_attention_case([1] * B, C, peaks),
+        f"diff_prepare_t{T}": diff_prepare_case(T, peaks), f"diff_prepare_t{B}": diff_prepare_case(B, peaks),
+        f"table_experts_prefill_t{T}": table_experts_case(T, peaks), f"table_experts_decode_b{B}": table_experts_case(B, peaks),
+    }
+    from .config import LlamaConfig
+    like = kb.headline_kernels(LlamaConfig.from_dict(lotirax_llama_config(n_runs)), B, C, T, peaks)
+    ops.check_kernel_errors()
+    res["llama_kernels"] = {k: v for k, v in like.items() if "attention" in k or "gate_up" in k or "down" in k}
+    return res
+
+
 def run(args, peaks) -> dict:
     n_layers = 3 * args.layers_per_kind
     res = {"deganex": model_throughput(deganex_config(args.layers_per_kind), args.batch, args.ctx, args.prefill_tokens, args.steps, args.warmup),
@@ -220,6 +340,7 @@ def run(args, peaks) -> dict:
 
 def main(argv=None, peaks=None) -> int:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    ap.add_argument("--design", default="deganex", choices=["deganex", "lotirax"])
     ap.add_argument("--layers-per-kind", type=int, default=2)
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--ctx", type=int, default=1024)
@@ -228,11 +349,14 @@ def main(argv=None, peaks=None) -> int:
     ap.add_argument("--warmup", type=int, default=4)
     args, _ = ap.parse_known_args(argv)
     peaks = peaks or {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
-    res = run(args, peaks)
-    d = res["deganex"]
-    print(json.dumps({"metric": "deganex_decode_tokens_per_s", "value": d["decode_tok_s"], "unit": "tokens/s", "n_gpus": 1, "dtype": "bf16",
+    if args.design == "lotirax":
+        res, model = run_lotirax(args, peaks), f"Lotirax, width {WIDTH}, 4 layers of which 2 run twice"
+    else:
+        res, model = run(args, peaks), f"Deganex, width {WIDTH}, {3 * args.layers_per_kind} layers"
+    d = res[args.design]
+    print(json.dumps({"metric": f"{args.design}_decode_tokens_per_s", "value": d["decode_tok_s"], "unit": "tokens/s", "n_gpus": 1, "dtype": "bf16",
                       "data": "synthetic (random weights and tokens)", "peaks": peaks,
-                      "config": {"model": f"Deganex, width {WIDTH}, {3 * args.layers_per_kind} layers", "batch": args.batch, "ctx": args.ctx,
+                      "config": {"model": model, "batch": args.batch, "ctx": args.ctx,
                                  "prefill_tokens": args.prefill_tokens, "l2": "kernels alone rotate over buffers larger than L2"},
                       **res}))
     return 0
