@@ -199,7 +199,7 @@ extern "C" int qv_diff_attention_generic(void* out, int ld_out, const void* q, i
 // ---------------------------------------------------------------- tensor cores (bfloat16)
 // qv_diff_attention_tc       a CTA serves a tile of 16 * MW query rows of one segment and one head with 2 * MW warps: warps
 //                            0..MW-1 run map 1 and warps MW..2MW-1 map 2, each over 16 rows; blocks of 64 keys (both maps' key
-//                            entries and the values) come through a two-stage cp.async ring that both maps read; Q.K^T and P.V as
+//                            entries and the values) come through a cp.async ring of two or three stages that both maps read; Q.K^T and P.V as
 //                            mma.sync m16n8k16 with float32 sums, softmax in float32 (base 2); at the end map 2's warps leave
 //                            their normalised rows in shared memory and map 1's warps form a1 - lam * a2, the root mean square
 //                            over the head's values and the output.  Map and value sizes are padded with zeros up to the
@@ -230,7 +230,7 @@ __device__ __forceinline__ uint32_t dpack(float lo, float hi) {
   return *(uint32_t*)&h;
 }
 
-template <int NT, int DVT, int MW, bool GROUPED>
+template <int NT, int DVT, int MW, bool GROUPED, int STAGES>
 __global__ void __launch_bounds__(MW == 1 ? 128 : 64 * MW) diff_attention_tc_kernel(
     bf16* __restrict__ out, int ld_out, const bf16* __restrict__ q, int ld_q, const bf16* __restrict__ cache,
     const int* __restrict__ seg_q_start, const int* __restrict__ seg_pos0, const int* __restrict__ block_table, int max_blocks,
@@ -244,7 +244,7 @@ __global__ void __launch_bounds__(MW == 1 ? 128 : 64 * MW) diff_attention_tc_ker
   constexpr int STAGE = DIFF_KB * (LDK + LDV);            // elements of one stage (keys of both maps, then values)
   extern __shared__ __align__(16) unsigned char diff_smem[];
   bf16* Qs = (bf16*)diff_smem;                            // [TM][LDK]
-  bf16* ring = Qs + TM * LDK;                             // [2][STAGE]
+  bf16* ring = Qs + TM * LDK;                             // [STAGES][STAGE]
   pdl_wait();
   pdl_launch_dependents();
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -314,8 +314,11 @@ __global__ void __launch_bounds__(MW == 1 ? 128 : 64 * MW) diff_attention_tc_ker
       }
     }
   }
-  if (nb > 0) load_block(0, kb0);
-  asm volatile("cp.async.commit_group;" ::: "memory");
+#pragma unroll
+  for (int st = 0; st < STAGES - 1; ++st) {               // one group a stage, empty past the end, so that the counts below hold
+    if (st < nb) load_block(st, kb0 + st * DIFF_KB);
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  }
 
   const int gr = lane >> 2, tg = lane & 3;                // fragment row (and row + 8), column pair
   int lo[2], hi[2];
@@ -339,17 +342,17 @@ __global__ void __launch_bounds__(MW == 1 ? 128 : 64 * MW) diff_attention_tc_ker
   uint32_t qf[NT / 16][4];
 
   for (int b = 0; b < nb; ++b) {
-    if (b + 1 < nb) load_block((b + 1) & 1, kb0 + (b + 1) * DIFF_KB);
+    asm volatile("cp.async.wait_group %0;" ::"n"(STAGES - 2) : "memory");
+    __syncthreads();                         // block b has landed for everyone; the stage filled next was read a round ago
+    if (b + STAGES - 1 < nb) load_block((b + STAGES - 1) % STAGES, kb0 + (b + STAGES - 1) * DIFF_KB);
     asm volatile("cp.async.commit_group;" ::: "memory");
-    asm volatile("cp.async.wait_group 1;" ::: "memory");
-    __syncthreads();
     if (b == 0 && computes) {
 #pragma unroll
       for (int kc = 0; kc < NT / 16; ++kc) dldsm4(qf[kc], Qs + (r0 + (lane & 15)) * LDK + mp * NT + kc * 16 + (lane >> 4) * 8);
     }
     const int kb = kb0 + b * DIFF_KB;
     if (computes && kb <= w_hi && kb + DIFF_KB - 1 >= w_lo) {
-      const bf16* Ks = ring + (b & 1) * STAGE;
+      const bf16* Ks = ring + (b % STAGES) * STAGE;
       const bf16* Vs = Ks + DIFF_KB * LDK;
       float s[DIFF_KB / 8][4];
 #pragma unroll
@@ -422,9 +425,9 @@ __global__ void __launch_bounds__(MW == 1 ? 128 : 64 * MW) diff_attention_tc_ker
         }
       }
     }
-    __syncthreads();                         // the stage is free for the load after next
   }
   asm volatile("cp.async.wait_group 0;" ::: "memory");
+  __syncthreads();                           // all warps are past their last block: the ring is free
 #pragma unroll
   for (int r = 0; r < 2; ++r) {
     lrow[r] += __shfl_xor_sync(0xffffffffu, lrow[r], 1);
@@ -560,20 +563,24 @@ extern "C" int qv_diff_attention_tc(void* out, int ld_out, const void* q, int ld
   const int NT = diff_pad_n(n), DVT = diff_pad_dv(dv);
   const bool small = max_q_len <= 16;
   const int MW = small ? 1 : 4;
-  const size_t smem = (size_t)((16 * MW) * (2 * NT + 8) + 2 * DIFF_KB * (2 * NT + 8 + DVT + 8)) * sizeof(bf16);
+  // three stages where they fit beside a second CTA's (or, for the widest sizes, at all), else two
+  const size_t stage_bytes = (size_t)DIFF_KB * (2 * NT + 8 + DVT + 8) * sizeof(bf16), q_bytes = (size_t)(16 * MW) * (2 * NT + 8) * sizeof(bf16);
+  const int stages = q_bytes + 3 * stage_bytes <= 200 * 1024 ? 3 : 2;
+  const size_t smem = q_bytes + stages * stage_bytes;
   const float scale_log2 = scale * 1.4426950408889634f;
   int page_shift = -1;
   if ((page & (page - 1)) == 0) for (page_shift = 0; (1 << page_shift) < page; ++page_shift) {}
   if (splits < 1) splits = 1;
   const dim3 grid(grouped ? splits : (max_q_len + 16 * MW - 1) / (16 * MW), S, grouped ? G : H);
   int rc = QV_ERR_UNSUPPORTED;
-#define DIFF_LAUNCH(N_, DV_, MW_, GR_)                                                                                              \
+#define DIFF_LAUNCH_ST(N_, DV_, MW_, GR_, ST_)                                                                                      \
   do {                                                                                                                              \
-    cudaFuncSetAttribute(diff_attention_tc_kernel<N_, DV_, MW_, GR_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);      \
-    rc = qv_launch(diff_attention_tc_kernel<N_, DV_, MW_, GR_>, grid, dim3(MW_ == 1 ? 128 : 64 * MW_), smem, st, (bf16*)out, ld_out, \
-                   (const bf16*)q, ld_q, (const bf16*)cache, seg_q_start, seg_pos0, block_table, max_blocks, H, G, n, dv, page,     \
-                   page_shift, window, scale_log2, lam, eps, post, partial, splits);                                                \
+    cudaFuncSetAttribute(diff_attention_tc_kernel<N_, DV_, MW_, GR_, ST_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+    rc = qv_launch(diff_attention_tc_kernel<N_, DV_, MW_, GR_, ST_>, grid, dim3(MW_ == 1 ? 128 : 64 * MW_), smem, st, (bf16*)out,   \
+                   ld_out, (const bf16*)q, ld_q, (const bf16*)cache, seg_q_start, seg_pos0, block_table, max_blocks, H, G, n, dv,   \
+                   page, page_shift, window, scale_log2, lam, eps, post, partial, splits);                                          \
   } while (0)
+#define DIFF_LAUNCH(N_, DV_, MW_, GR_) do { if (stages == 3) DIFF_LAUNCH_ST(N_, DV_, MW_, GR_, 3); else DIFF_LAUNCH_ST(N_, DV_, MW_, GR_, 2); } while (0)
 #define DIFF_BY_MW(N_, DV_)                                                   \
   do {                                                                        \
     if (grouped) DIFF_LAUNCH(N_, DV_, 1, true);                               \
@@ -585,6 +592,7 @@ extern "C" int qv_diff_attention_tc(void* out, int ld_out, const void* q, int ld
 #undef DIFF_BY_DV
 #undef DIFF_BY_MW
 #undef DIFF_LAUNCH
+#undef DIFF_LAUNCH_ST
   if (rc || splits <= 1) return rc;
   const int T = S;                                        // single tokens: a segment is a token
   const dim3 mgrid((T * H + 3) / 4);
