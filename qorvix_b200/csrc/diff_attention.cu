@@ -198,8 +198,8 @@ extern "C" int qv_diff_attention_generic(void* out, int ld_out, const void* q, i
 
 // ---------------------------------------------------------------- tensor cores (bfloat16)
 // qv_diff_attention_tc       a CTA serves a tile of 16 * MW query rows of one segment and one head with 2 * MW warps: warps
-//                            0..MW-1 run map 1 and warps MW..2MW-1 map 2, each over 16 rows; blocks of 64 keys (both maps' key
-//                            entries and the values) come through a cp.async ring of two or three stages that both maps read; Q.K^T and P.V as
+//                            0..MW-1 run map 1 and warps MW..2MW-1 map 2, each over 16 rows; blocks of 32 keys (both maps' key
+//                            entries and the values) come through a cp.async ring of four stages that both maps read; Q.K^T and P.V as
 //                            mma.sync m16n8k16 with float32 sums, softmax in float32 (base 2); at the end map 2's warps leave
 //                            their normalised rows in shared memory and map 1's warps form a1 - lam * a2, the root mean square
 //                            over the head's values and the output.  Map and value sizes are padded with zeros up to the
@@ -207,7 +207,7 @@ extern "C" int qv_diff_attention_generic(void* out, int ld_out, const void* q, i
 //                            Single query tokens take a tile whose rows are the query heads of one key/value head (the keys are
 //                            read once for the group); their keys may be cut into slices (grid.x = slices): the two maps'
 //                            running maxima, sums and unnormalised rows then go to a workspace that the merge kernel finishes.
-#define DIFF_KB 64
+#define DIFF_KB 32
 
 __device__ __forceinline__ void dcp_async16(void* smem, const void* gmem, int bytes) {
   const uint32_t s = (uint32_t)__cvta_generic_to_shared(smem);
@@ -231,14 +231,14 @@ __device__ __forceinline__ uint32_t dpack(float lo, float hi) {
 }
 
 template <int NT, int DVT, int MW, bool GROUPED, int STAGES>
-__global__ void __launch_bounds__(MW == 1 ? 128 : 64 * MW) diff_attention_tc_kernel(
+__global__ void __launch_bounds__(MW == 1 ? 128 : 64 * MW, MW == 1 ? 1 : (DVT <= 128 ? 2 : 1)) diff_attention_tc_kernel(
     bf16* __restrict__ out, int ld_out, const bf16* __restrict__ q, int ld_q, const bf16* __restrict__ cache,
     const int* __restrict__ seg_q_start, const int* __restrict__ seg_pos0, const int* __restrict__ block_table, int max_blocks,
     int H, int G, int n, int dv, int page, int page_shift, int window, float scale_log2, float lam, float eps, float post,
     float* __restrict__ partial, int splits) {
   // GROUPED (single query tokens, MW == 1): the tile's rows are the query heads of one key/value head, which all see the
-  // same keys, so those are read once for the group; grid (slices, tokens, key/value heads).  Else the rows are tokens of
-  // one segment and one head; grid (tiles, segments, heads).  With MW == 1 two more warps only help to copy.
+  // same keys, so those are read once for the group.  Else the rows are tokens of one segment and one head.  With MW == 1
+  // two more warps only help to copy.
   constexpr int TM = 16 * MW, THREADS = MW == 1 ? 128 : 64 * MW, NWARPS = THREADS / 32;
   constexpr int LDK = 2 * NT + 8, LDV = DVT + 8;          // padded rows: ldmatrix without bank conflicts
   constexpr int STAGE = DIFF_KB * (LDK + LDV);            // elements of one stage (keys of both maps, then values)
@@ -252,10 +252,12 @@ __global__ void __launch_bounds__(MW == 1 ? 128 : 64 * MW) diff_attention_tc_ker
   const int mp = computes ? warp / MW : 0, r0 = (warp % MW) * 16;        // this warp's map and first row of the tile
   const int seg = blockIdx.y;
   const int hpg = H / G;
-  const int g = GROUPED ? blockIdx.z : blockIdx.z / hpg;
-  const int h = GROUPED ? g * hpg : blockIdx.z;           // the (first) head of the tile
+  // grouped: grid (slices, tokens, key/value heads); else (heads, segments, tiles) with the last tiles of the segments,
+  // which see the most keys, first in the order CTAs are handed out, so that the short ones fill the SMs at the end
+  const int g = GROUPED ? blockIdx.z : blockIdx.x / hpg;
+  const int h = GROUPED ? g * hpg : blockIdx.x;           // the (first) head of the tile
   const int q0 = seg_q_start[seg], len = seg_q_start[seg + 1] - q0;
-  const int row0 = GROUPED ? 0 : blockIdx.x * TM;
+  const int row0 = GROUPED ? 0 : (gridDim.z - 1 - blockIdx.z) * TM;
   if (!GROUPED && row0 >= len) return;
   const int rows = GROUPED ? hpg : (len - row0 < TM ? len - row0 : TM);
   const int pos0 = seg_pos0[seg] + row0;                  // position of the tile's first row
@@ -272,38 +274,55 @@ __global__ void __launch_bounds__(MW == 1 ? 128 : 64 * MW) diff_attention_tc_ker
     nb = b_hi - b_lo;                                     // may be <= 0: an empty slice leaves an empty partial
   }
 
-  // a warp copies whole key rows: the row's place is worked out once, by all lanes alike, then every lane takes pieces
+  // A warp copies whole key rows, every lane its own 16-byte pieces of the row: where a lane's pieces lie in the row and
+  // in a stage is worked out once; per key only the row's address is left to find.
+  constexpr int KC = 2 * NT / 8, VC = DVT / 8;            // 16-byte pieces of a key row (both maps) and of a value row
+  constexpr int NP = (KC + VC + 31) / 32;                 // pieces a lane copies per key
+  int piece_src[NP], piece_dst[NP], piece_ld[NP];         // element offset in the cache row (-1: zeros), in the stage, stage row length
+#pragma unroll
+  for (int i = 0; i < NP; ++i) {
+    const int cc = lane + 32 * i;
+    piece_src[i] = -1;
+    piece_dst[i] = 0;
+    piece_ld[i] = 0;
+    if (cc < KC) {
+      const int m = (cc * 8) / NT, within = cc * 8 - m * NT;
+      if (within < n) piece_src[i] = g * 2 * n + m * n + within;
+      piece_dst[i] = cc * 8;
+      piece_ld[i] = LDK;
+    } else if (cc < KC + VC) {
+      const int col = (cc - KC) * 8;
+      if (col < dv) piece_src[i] = G * 2 * n + g * dv + col;
+      piece_dst[i] = DIFF_KB * LDK + col;
+      piece_ld[i] = LDV;
+    }
+  }
   auto load_block = [&](int stage, int kb) {
-    bf16* Ks = ring + stage * STAGE;
-    bf16* Vs = Ks + DIFF_KB * LDK;
-    constexpr int KC = 2 * NT / 8, VC = DVT / 8;          // 16-byte pieces of a key row (both maps) and of a value row
+    bf16* base = ring + stage * STAGE;
+    // the block's page numbers in one load (lane l: key kb + l), handed out by shuffles: a look-up per key would
+    // put a round trip to memory ahead of every row's copies
+    static_assert(DIFF_KB == 32, "one lane a key");
+    int page_of_lane = 0;
+    {
+      const int key = kb + lane;
+      if (key >= kmin && key <= kmax) page_of_lane = bt[page_shift >= 0 ? key >> page_shift : key / page];
+    }
     for (int j = warp; j < DIFF_KB; j += NWARPS) {
       const int key = kb + j;
       const bool kin = key >= kmin && key <= kmax;
-      const bf16* row = cache;
-      if (kin) {
-        const int pg = page_shift >= 0 ? key >> page_shift : key / page;
-        const int in_page = page_shift >= 0 ? key & (page - 1) : key - pg * page;
-        row = cache + ((size_t)bt[pg] * page + (size_t)in_page) * width;
-      }
-      const bf16* krow = row + (size_t)g * 2 * n;
-      const bf16* vrow = row + (size_t)G * 2 * n + (size_t)g * dv;
+      const int page_id = __shfl_sync(0xffffffffu, page_of_lane, j);
+      const int in_page = page_shift >= 0 ? key & (page - 1) : key % page;
+      const bf16* row = cache + ((size_t)page_id * page + (size_t)in_page) * width;       // a key outside the range reads nothing
 #pragma unroll
-      for (int cc = lane; cc < KC + VC; cc += 32) {
-        if (cc < KC) {
-          const int m = (cc * 8) / NT, within = cc * 8 - m * NT;
-          const bool ok = kin && within < n;
-          dcp_async16(Ks + j * LDK + cc * 8, ok ? krow + m * n + within : cache, ok ? 16 : 0);
-        } else {
-          const int col = (cc - KC) * 8;
-          const bool ok = kin && col < dv;
-          dcp_async16(Vs + j * LDV + col, ok ? vrow + col : cache, ok ? 16 : 0);
+      for (int i = 0; i < NP; ++i) {
+        if (NP * 32 == KC + VC || lane + 32 * i < KC + VC) {
+          const bool ok = kin && piece_src[i] >= 0;
+          dcp_async16(base + j * piece_ld[i] + piece_dst[i], ok ? row + piece_src[i] : cache, ok ? 16 : 0);
         }
       }
     }
   };
   {   // the tile's queries, both maps, zero-padded
-    constexpr int KC = 2 * NT / 8;
     for (int r = warp; r < TM; r += NWARPS) {
       const bf16* qrow = GROUPED ? q + (size_t)q0 * ld_q + (size_t)(h + r) * 2 * n : q + (size_t)(q0 + row0 + r) * ld_q + (size_t)h * 2 * n;
 #pragma unroll
@@ -339,17 +358,12 @@ __global__ void __launch_bounds__(MW == 1 ? 128 : 64 * MW) diff_attention_tc_ker
 #pragma unroll
   for (int i = 0; i < DVT / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
   float mrow[2] = {-INFINITY, -INFINITY}, lrow[2] = {0.f, 0.f};
-  uint32_t qf[NT / 16][4];
 
   for (int b = 0; b < nb; ++b) {
     asm volatile("cp.async.wait_group %0;" ::"n"(STAGES - 2) : "memory");
     __syncthreads();                         // block b has landed for everyone; the stage filled next was read a round ago
     if (b + STAGES - 1 < nb) load_block((b + STAGES - 1) % STAGES, kb0 + (b + STAGES - 1) * DIFF_KB);
     asm volatile("cp.async.commit_group;" ::: "memory");
-    if (b == 0 && computes) {
-#pragma unroll
-      for (int kc = 0; kc < NT / 16; ++kc) dldsm4(qf[kc], Qs + (r0 + (lane & 15)) * LDK + mp * NT + kc * 16 + (lane >> 4) * 8);
-    }
     const int kb = kb0 + b * DIFF_KB;
     if (computes && kb <= w_hi && kb + DIFF_KB - 1 >= w_lo) {
       const bf16* Ks = ring + (b % STAGES) * STAGE;
@@ -359,12 +373,14 @@ __global__ void __launch_bounds__(MW == 1 ? 128 : 64 * MW) diff_attention_tc_ker
       for (int i = 0; i < DIFF_KB / 8; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
 #pragma unroll
       for (int kc = 0; kc < NT / 16; ++kc) {
+        uint32_t qf[4];                      // the queries' fragments come from shared memory block by block: registers are what limits the CTAs an SM holds
+        dldsm4(qf, Qs + (r0 + (lane & 15)) * LDK + mp * NT + kc * 16 + (lane >> 4) * 8);
 #pragma unroll
         for (int pr = 0; pr < DIFF_KB / 16; ++pr) {
           uint32_t bfr[4];
           dldsm4(bfr, Ks + (pr * 16 + (lane >> 4) * 8 + (lane & 7)) * LDK + mp * NT + kc * 16 + ((lane >> 3) & 1) * 8);
-          dmma(s[2 * pr], qf[kc], bfr[0], bfr[1]);
-          dmma(s[2 * pr + 1], qf[kc], bfr[2], bfr[3]);
+          dmma(s[2 * pr], qf, bfr[0], bfr[1]);
+          dmma(s[2 * pr + 1], qf, bfr[2], bfr[3]);
         }
       }
       float mx[2] = {-INFINITY, -INFINITY};
@@ -410,8 +426,10 @@ __global__ void __launch_bounds__(MW == 1 ? 128 : 64 * MW) diff_attention_tc_ker
           lrow[r] += p;
         }
       }
+      if (!__all_sync(0xffffffffu, corr[0] == 1.f && corr[1] == 1.f)) {      // no row's maximum moved: nothing to scale down
 #pragma unroll
-      for (int i = 0; i < DVT / 8; ++i) { o[i][0] *= corr[0]; o[i][1] *= corr[0]; o[i][2] *= corr[1]; o[i][3] *= corr[1]; }
+        for (int i = 0; i < DVT / 8; ++i) { o[i][0] *= corr[0]; o[i][1] *= corr[0]; o[i][2] *= corr[1]; o[i][3] *= corr[1]; }
+      }
 #pragma unroll
       for (int kc = 0; kc < DIFF_KB / 16; ++kc) {
         uint32_t a[4] = {dpack(s[2 * kc][0], s[2 * kc][1]), dpack(s[2 * kc][2], s[2 * kc][3]),
@@ -563,15 +581,19 @@ extern "C" int qv_diff_attention_tc(void* out, int ld_out, const void* q, int ld
   const int NT = diff_pad_n(n), DVT = diff_pad_dv(dv);
   const bool small = max_q_len <= 16;
   const int MW = small ? 1 : 4;
-  // three stages where they fit beside a second CTA's (or, for the widest sizes, at all), else two
+  // four stages of 32 keys (the widest sizes: 169 KB, one CTA an SM, which their registers allow anyway); the ring must
+  // also hold map 2's float32 rows at the end
   const size_t stage_bytes = (size_t)DIFF_KB * (2 * NT + 8 + DVT + 8) * sizeof(bf16), q_bytes = (size_t)(16 * MW) * (2 * NT + 8) * sizeof(bf16);
-  const int stages = q_bytes + 3 * stage_bytes <= 200 * 1024 ? 3 : 2;
-  const size_t smem = q_bytes + stages * stage_bytes;
+  constexpr int stages = 4;
+  const size_t rows_bytes = (size_t)(16 * MW) * (DVT + 1) * sizeof(float);
+  const size_t smem = q_bytes + (stages * stage_bytes > rows_bytes ? stages * stage_bytes : rows_bytes);
   const float scale_log2 = scale * 1.4426950408889634f;
   int page_shift = -1;
   if ((page & (page - 1)) == 0) for (page_shift = 0; (1 << page_shift) < page; ++page_shift) {}
   if (splits < 1) splits = 1;
-  const dim3 grid(grouped ? splits : (max_q_len + 16 * MW - 1) / (16 * MW), S, grouped ? G : H);
+  const int tiles = (max_q_len + 16 * MW - 1) / (16 * MW);
+  if (!grouped && tiles > 65535) return QV_ERR_TOO_LARGE;
+  const dim3 grid(grouped ? splits : H, S, grouped ? G : tiles);
   int rc = QV_ERR_UNSUPPORTED;
 #define DIFF_LAUNCH_ST(N_, DV_, MW_, GR_, ST_)                                                                                      \
   do {                                                                                                                              \
@@ -580,7 +602,7 @@ extern "C" int qv_diff_attention_tc(void* out, int ld_out, const void* q, int ld
                    ld_out, (const bf16*)q, ld_q, (const bf16*)cache, seg_q_start, seg_pos0, block_table, max_blocks, H, G, n, dv,   \
                    page, page_shift, window, scale_log2, lam, eps, post, partial, splits);                                          \
   } while (0)
-#define DIFF_LAUNCH(N_, DV_, MW_, GR_) do { if (stages == 3) DIFF_LAUNCH_ST(N_, DV_, MW_, GR_, 3); else DIFF_LAUNCH_ST(N_, DV_, MW_, GR_, 2); } while (0)
+#define DIFF_LAUNCH(N_, DV_, MW_, GR_) DIFF_LAUNCH_ST(N_, DV_, MW_, GR_, stages)
 #define DIFF_BY_MW(N_, DV_)                                                   \
   do {                                                                        \
     if (grouped) DIFF_LAUNCH(N_, DV_, 1, true);                               \

@@ -397,8 +397,9 @@ def diff_attention_splits(tokens: int, H: int, G: int, window: int, max_ctx: int
     if H // G > 16:
         return 1
     keys = min(window, max_ctx) if window > 0 else max_ctx
-    blocks = max(1, -(-keys // 64))
-    return max(1, min(2 * sm_count() // max(tokens * G, 1), blocks, 32))
+    blocks = max(1, -(-keys // 32))                  # the kernel's blocks of keys
+    # about one CTA an SM, at least two blocks a slice, at most twelve slices (the merge reads them one after another)
+    return max(1, min(sm_count() // max(tokens * G, 1), blocks // 2, 12))
 
 
 def diff_attention(out, q, cache_layer, ctx, block_table, H, G, n, dv, page, window, scale, lam, eps, post) -> None:

@@ -20,14 +20,14 @@ def spec_of(raw):
 
 
 def test_config_round_trip_and_registry():
-    for raw in (lh.CONFIG_A, lh.CONFIG_B, lh.CONFIG_C):
+    for raw in (lh.CONFIG_A, lh.CONFIG_B, lh.CONFIG_C, lh.CONFIG_D):
         cfg, _ = spec_of(raw)
         assert isinstance(cfg, LotiraxConfig) and cfg.to_dict() == json.loads(json.dumps(raw))
         assert cfg.vocab_size == raw["vocab"] and cfg.residual_mult == raw["residual_mult"]
 
 
 @pytest.mark.parametrize("raw,order,first", [(lh.CONFIG_A, [0, 1, 2, 1, 2, 3], (1, 3)), (lh.CONFIG_B, [0, 1, 2], None),
-                                             (lh.CONFIG_C, [0, 1, 0, 1, 0, 1], (0, 2, 4))])
+                                             (lh.CONFIG_C, [0, 1, 0, 1, 0, 1], (0, 2, 4)), (lh.CONFIG_D, [0, 1], (1,))])
 def test_order_of_runs_and_re_entries(raw, order, first):
     _, spec = spec_of(raw)
     assert spec.order == order
@@ -37,7 +37,7 @@ def test_order_of_runs_and_re_entries(raw, order, first):
 
 
 def test_tensor_table_matches_the_weights_the_helpers_draw():
-    for raw in (lh.CONFIG_A, lh.CONFIG_B, lh.CONFIG_C):
+    for raw in (lh.CONFIG_A, lh.CONFIG_B, lh.CONFIG_C, lh.CONFIG_D):
         _, spec = spec_of(raw)
         drawn = {k: tuple(v.shape) for k, v in lh.model_weights(raw, 1).items()}
         assert spec.expected_shapes() == drawn

@@ -87,7 +87,8 @@ MIXER_CASES = [lh.attn(), lh.attn(heads=3, kv_heads=3, dim=20, vdim=12, window=9
                lh.attn(heads=5, kv_heads=5, dim=12, vdim=28, window=64, rot_dims=12, scaling={"factor": 8.0, "original": 16, "fast": 4.0, "slow": 0.5}),
                lh.attn(heads=4, kv_heads=2, dim=32, vdim=64, window=33, rot_dims=32), lh.attn(heads=8, kv_heads=2, dim=64, vdim=128, window=0, rot_dims=32),
                lh.attn(heads=4, kv_heads=4, dim=16, vdim=32, window=48, rot_dims=16), lh.attn(heads=2, kv_heads=2, dim=48, vdim=96, window=20, rot_dims=48),
-               lh.attn(heads=3, kv_heads=1, dim=7, vdim=70, window=5, rot_dims=6)]
+               lh.attn(heads=3, kv_heads=1, dim=7, vdim=70, window=5, rot_dims=6),
+               lh.attn(heads=34, kv_heads=2, dim=8, vdim=8, window=30, rot_dims=8)]      # 17 query heads a key/value head: no shared tile
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
@@ -230,7 +231,7 @@ def test_stream_re_entry_alone(dtype):
 @pytest.fixture(scope="module")
 def models():
     out = {}
-    for name, cfg in (("A", lh.CONFIG_A), ("B", lh.CONFIG_B), ("C", lh.CONFIG_C)):
+    for name, cfg in (("A", lh.CONFIG_A), ("B", lh.CONFIG_B), ("C", lh.CONFIG_C), ("D", lh.CONFIG_D)):
         d = lh.make_model_dir(cfg, seed=11 + len(out))
         out[name] = (d, cfg, lh.as_float64(lh.model_weights(cfg, seed=11 + len(out))), {})
     return out
@@ -253,7 +254,7 @@ def runner(model, dtype, max_tokens=256, **kw):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 def test_whole_prompts_and_the_stream_after_every_run(models, name, dtype):
     m = models[name]
     r = runner(m, dtype, use_graphs=False)          # the tap copies to the host, which a captured step cannot
@@ -273,7 +274,7 @@ def test_whole_prompts_and_the_stream_after_every_run(models, name, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 @pytest.mark.parametrize("graphs", [True, False])
 def test_prefill_then_long_decode(models, name, dtype, graphs):
     m = models[name]
@@ -287,7 +288,7 @@ def test_prefill_then_long_decode(models, name, dtype, graphs):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 def test_portions_of_many_sizes(models, name, dtype):
     m = models[name]
     toks = tokens(m[1]["vocab"], 120, 31)
@@ -304,7 +305,7 @@ def test_portions_of_many_sizes(models, name, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 def test_mixed_batches_with_pages_and_slots_used_again(models, name, dtype):
     """Four requests of unequal length advance in unequal portions beside one another in a pool that holds little more
     than they need; two end early and two new ones take their slots and pages.  Every row equals the request alone."""
@@ -356,7 +357,7 @@ def test_logits_do_not_depend_on_the_batch(models, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 def test_greedy_generation_through_the_scheduler(models, name, dtype):
     m = models[name]
     V = m[1]["vocab"]
