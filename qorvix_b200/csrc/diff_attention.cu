@@ -2,8 +2,8 @@
 //   a_m = softmax_j((q_m . k_m,j) * scale) V      for the two maps m = 1, 2 (causal, optionally the last `window` keys),
 //   o = a_1 - lam * a_2;   out = o / sqrt(mean(o^2) + eps) * post            (mean over the head's value entries).
 //
-// qv_diff_prepare            per token: bias added to the projection's sums, every map of q and k divided by its root
-//                            mean square and weighted, the first `rot` entries of each map rotated (pairs i, i + rot/2,
+// qv_diff_prepare            per token (a CTA): bias added to the projection's sums, every map of q and k divided by its
+//                            root mean square and weighted, the first `rot` entries of each map rotated (pairs i, i + rot/2,
 //                            cos/sin from a table row of the token's position); q goes to a dense buffer, k and v (with
 //                            its bias) to the token's cache row [k: G x 2n | v: G x dv].  All arithmetic float32.
 // qv_diff_attention_generic  one warp per (token, head), float32 arithmetic whatever the storage type, any sizes; keys in
@@ -13,6 +13,9 @@
 
 #define DIFF_MAX_DV 512
 
+// A CTA serves a token (or, in steps of few tokens, a share of a token's maps): the token's row of the projection (plus bias)
+// is brought into shared memory by all threads at once, then every warp takes maps of q and k (norm, weight, rotation) and
+// heads of v in turn and writes them out.
 template <typename TP, typename T>
 __global__ void __launch_bounds__(256) diff_prepare_kernel(T* __restrict__ q_out, int ld_q, const TP* __restrict__ proj, int ld_p,
                                                            const float* __restrict__ bias, const float* __restrict__ qw,
@@ -20,12 +23,25 @@ __global__ void __launch_bounds__(256) diff_prepare_kernel(T* __restrict__ q_out
                                                            int table_rows, const int* __restrict__ tok_pos, const int* __restrict__ tok_seg,
                                                            const int* __restrict__ block_table, int max_blocks, T* __restrict__ cache,
                                                            int H, int G, int n, int dv, int rot, int page) {
+  extern __shared__ float prep_row[];                        // the token's (H + G) * 2n + G * dv sums, bias added
   pdl_wait();
   pdl_launch_dependents();
-  const int t = blockIdx.x, lane = threadIdx.x & 31;
-  const int unit = blockIdx.y * 8 + (threadIdx.x >> 5);      // 2H maps of q, 2G maps of k, G heads of v
+  const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int nq = 2 * H, nk = 2 * G;
-  if (unit >= nq + nk + G) return;
+  const int cols = (nq + nk) * n + G * dv;
+  const TP* prow = proj + (size_t)t * ld_p;
+  if (sizeof(TP) == 4 && (cols & 3) == 0 && (ld_p & 3) == 0 && (((uintptr_t)proj | (uintptr_t)bias) & 15) == 0) {
+    for (int i = threadIdx.x * 4; i < cols; i += 256 * 4) {
+      float4 v = *(const float4*)((const float*)prow + i);
+      if (bias) {
+        const float4 bv = *(const float4*)(bias + i);
+        v.x += bv.x; v.y += bv.y; v.z += bv.z; v.w += bv.w;
+      }
+      *(float4*)(prep_row + i) = v;
+    }
+  } else {
+    for (int i = threadIdx.x; i < cols; i += 256) prep_row[i] = to_f(prow[i]) + (bias ? bias[i] : 0.f);
+  }
   const int pos = tok_pos[t];
   const size_t width = (size_t)G * (2 * n + dv);
   T* crow = nullptr;
@@ -33,38 +49,35 @@ __global__ void __launch_bounds__(256) diff_prepare_kernel(T* __restrict__ q_out
     const int pg = block_table[(size_t)tok_seg[t] * max_blocks + pos / page];
     crow = cache + ((size_t)pg * page + pos % page) * width;
   }
-  const TP* prow = proj + (size_t)t * ld_p;
-  if (unit < nq + nk) {
-    const bool is_q = unit < nq;
-    if (!is_q && !crow) return;
-    const int col0 = unit * n;                               // the k maps follow the q maps in the projection's columns
-    const TP* src = prow + col0;
-    const float* b = bias ? bias + col0 : nullptr;
-    float ss = 0.f;
-    for (int i = lane; i < n; i += 32) {
-      const float x = to_f(src[i]) + (b ? b[i] : 0.f);
-      ss = fmaf(x, x, ss);
+  const int half = rot >> 1;
+  const float2* cs = cos_sin ? cos_sin + (size_t)(pos < table_rows ? pos : table_rows - 1) * half : nullptr;
+  __syncthreads();
+  for (int unit = blockIdx.y * 8 + warp; unit < nq + nk + G; unit += 8 * gridDim.y) {     // 2H maps of q, 2G maps of k, G heads of v
+    if (unit < nq + nk) {
+      const bool is_q = unit < nq;
+      if (!is_q && !crow) continue;
+      const int col0 = unit * n;                             // the k maps follow the q maps in the projection's columns
+      const float* src = prep_row + col0;
+      float ss = 0.f;
+      for (int i = lane; i < n; i += 32) ss = fmaf(src[i], src[i], ss);
+      ss = warp_sum(ss);
+      const float inv = 1.0f / sqrtf(ss / (float)n + eps);
+      const float* w = is_q ? qw : kw;
+      T* dst = is_q ? q_out + (size_t)t * ld_q + col0 : crow + (size_t)(unit - nq) * n;
+      for (int i = lane; i < half; i += 32) {
+        const float u = src[i] * inv * w[i];
+        const float v = src[i + half] * inv * w[i + half];
+        const float2 c = cs[i];
+        dst[i] = from_f<T>(u * c.x - v * c.y);
+        dst[i + half] = from_f<T>(v * c.x + u * c.y);
+      }
+      for (int i = rot + lane; i < n; i += 32) dst[i] = from_f<T>(src[i] * inv * w[i]);
+    } else if (crow) {
+      const int vh = unit - nq - nk;
+      const float* src = prep_row + (nq + nk) * n + vh * dv;
+      T* dst = crow + (size_t)G * 2 * n + (size_t)vh * dv;
+      for (int i = lane; i < dv; i += 32) dst[i] = from_f<T>(src[i]);
     }
-    ss = warp_sum(ss);
-    const float inv = 1.0f / sqrtf(ss / (float)n + eps);
-    const float* w = is_q ? qw : kw;
-    T* dst = is_q ? q_out + (size_t)t * ld_q + col0 : crow + (size_t)(unit - nq) * n;
-    const int half = rot >> 1;
-    const float2* cs = cos_sin ? cos_sin + (size_t)(pos < table_rows ? pos : table_rows - 1) * half : nullptr;
-    for (int i = lane; i < half; i += 32) {
-      const float u = (to_f(src[i]) + (b ? b[i] : 0.f)) * inv * w[i];
-      const float v = (to_f(src[i + half]) + (b ? b[i + half] : 0.f)) * inv * w[i + half];
-      const float2 c = cs[i];
-      dst[i] = from_f<T>(u * c.x - v * c.y);
-      dst[i + half] = from_f<T>(v * c.x + u * c.y);
-    }
-    for (int i = rot + lane; i < n; i += 32) dst[i] = from_f<T>((to_f(src[i]) + (b ? b[i] : 0.f)) * inv * w[i]);
-  } else if (crow) {
-    const int vh = unit - nq - nk;
-    const int col0 = (nq + nk) * n + vh * dv;
-    const TP* src = prow + col0;
-    T* dst = crow + (size_t)G * 2 * n + (size_t)vh * dv;
-    for (int i = lane; i < dv; i += 32) dst[i] = from_f<T>(to_f(src[i]) + (bias ? bias[col0 + i] : 0.f));
   }
 }
 
@@ -74,13 +87,19 @@ extern "C" int qv_diff_prepare(void* q_out, int ld_q, const void* proj, int ld_p
                                int proj_dt, int dt, void* stream) {
   if (T <= 0) return 0;
   if (rot < 0 || rot > n || (rot & 1) || (rot > 0 && !cos_sin) || H <= 0 || G <= 0) return QV_ERR_UNSUPPORTED;
-  const int units = 2 * H + 3 * G;
-  if ((units + 7) / 8 > 65535) return QV_ERR_TOO_LARGE;
-  const dim3 grid(T, (units + 7) / 8);
+  const size_t smem = (size_t)((H + G) * 2 * n + G * dv) * sizeof(float);
+  if (smem > 200 * 1024) return QV_ERR_TOO_LARGE;
   cudaStream_t st = (cudaStream_t)stream;
+  // few tokens: a token's maps are spread over several CTAs (each brings the row in for itself), so that the step fills more SMs
+  const int units = 2 * H + 3 * G;
+  const int spread = T <= 32 ? ((units + 7) / 8 < 65535 ? (units + 7) / 8 : 65535) : 1;
 #define PREP(TP, TT)                                                                                                              \
-  return qv_launch(diff_prepare_kernel<TP, TT>, grid, dim3(256), 0, st, (TT*)q_out, ld_q, (const TP*)proj, ld_p, bias, qw, kw, eps, \
-                   (const float2*)cos_sin, table_rows, tok_pos, tok_seg, block_table, max_blocks, (TT*)cache, H, G, n, dv, rot, page)
+  do {                                                                                                                            \
+    if (smem > 48 * 1024) cudaFuncSetAttribute(diff_prepare_kernel<TP, TT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+    return qv_launch(diff_prepare_kernel<TP, TT>, dim3(T, spread), dim3(256), smem, st, (TT*)q_out, ld_q, (const TP*)proj, ld_p, bias, qw, kw, \
+                     eps, (const float2*)cos_sin, table_rows, tok_pos, tok_seg, block_table, max_blocks, (TT*)cache, H, G, n, dv, rot, \
+                     page);                                                                                                       \
+  } while (0)
   if (proj_dt == QV_DT_F32 && dt == QV_DT_F32) PREP(float, float);
   if (proj_dt == QV_DT_F32 && dt == QV_DT_BF16) PREP(float, bf16);
   if (proj_dt == QV_DT_BF16 && dt == QV_DT_BF16) PREP(bf16, bf16);
@@ -509,7 +528,8 @@ __global__ void __launch_bounds__(MW == 1 ? 128 : 64 * MW, MW == 1 ? 1 : (DVT <=
 }
 
 // Finishes single tokens whose keys were cut into slices: per (token, head) the slices' maxima, sums and rows of both maps
-// are merged in the order of the slices, then o = a1 - lam * a2, the root mean square over dv, the output.  One warp each.
+// are merged, then o = a1 - lam * a2, the root mean square over dv, the output.  One warp each; lane s holds slice s's
+// maximum and sum (at most 32 slices), and the rows are fetched four slices at a time so that their loads overlap.
 template <int DVT>
 __global__ void __launch_bounds__(128) diff_merge_kernel(bf16* __restrict__ out, int ld_out, const float* __restrict__ partial, int T, int H,
                                                          int dv, int splits, float lam, float eps, float post) {
@@ -520,25 +540,39 @@ __global__ void __launch_bounds__(128) diff_merge_kernel(bf16* __restrict__ out,
   if (idx >= T * H) return;
   const int t = idx / H, h = idx - t * H;
   constexpr int NR = DVT / 32;
-  float a[2][NR];
+  constexpr size_t STRIDE = 2 * (DVT + 2);                 // floats from a slice to the next (both maps)
+  const float* base = partial + (size_t)idx * splits * STRIDE;
+  float wgt[2], a[2][NR];
 #pragma unroll
   for (int mp = 0; mp < 2; ++mp) {
-    const float* base = partial + (((size_t)idx * splits) * 2 + mp) * (DVT + 2);
-    float m = -INFINITY;
-    for (int s = 0; s < splits; ++s) m = fmaxf(m, base[(size_t)s * 2 * (DVT + 2)]);
-    float l = 0.f;
+    const float* p = base + (size_t)lane * STRIDE + mp * (DVT + 2);
+    const float ms = lane < splits ? p[0] : -INFINITY, ls = lane < splits ? p[1] : 0.f;
+    const float m = warp_max(ms);
+    wgt[mp] = ms == -INFINITY ? 0.f : exp2f(ms - m);
+    const float l = warp_sum(wgt[mp] * ls);               // a fixed order: the result does not depend on the batch
+    wgt[mp] *= l > 0.f ? 1.0f / l : 0.f;
 #pragma unroll
     for (int r = 0; r < NR; ++r) a[mp][r] = 0.f;
-    for (int s = 0; s < splits; ++s) {
-      const float* p = base + (size_t)s * 2 * (DVT + 2);
-      const float w = p[0] == -INFINITY ? 0.f : exp2f(p[0] - m);
-      l = fmaf(w, p[1], l);
+  }
+  for (int s0 = 0; s0 < splits; s0 += 4) {
+    float v[4][2][NR];
 #pragma unroll
-      for (int r = 0; r < NR; ++r) a[mp][r] = fmaf(w, p[2 + lane + 32 * r], a[mp][r]);
+    for (int u = 0; u < 4; ++u) {
+#pragma unroll
+      for (int mp = 0; mp < 2; ++mp) {
+#pragma unroll
+        for (int r = 0; r < NR; ++r) v[u][mp][r] = s0 + u < splits ? base[(size_t)(s0 + u) * STRIDE + mp * (DVT + 2) + 2 + lane + 32 * r] : 0.f;
+      }
     }
-    const float inv = l > 0.f ? 1.0f / l : 0.f;
 #pragma unroll
-    for (int r = 0; r < NR; ++r) a[mp][r] *= inv;
+    for (int u = 0; u < 4; ++u) {
+#pragma unroll
+      for (int mp = 0; mp < 2; ++mp) {
+        const float w = __shfl_sync(0xffffffffu, wgt[mp], (s0 + u) & 31);
+#pragma unroll
+        for (int r = 0; r < NR; ++r) a[mp][r] = fmaf(w, v[u][mp][r], a[mp][r]);
+      }
+    }
   }
   float ss = 0.f;
 #pragma unroll
@@ -575,7 +609,7 @@ extern "C" int qv_diff_attention_tc(void* out, int ld_out, const void* q, int ld
   if (n <= 0 || n > 128 || (n & 7) || dv <= 0 || dv > 256 || (dv & 7) || G <= 0 || H % G || (ld_q & 7) || (ld_out & 1) || page <= 0) return QV_ERR_UNSUPPORTED;
   if ((((uintptr_t)q | (uintptr_t)cache) & 15) || ((uintptr_t)out & 3) || ((G * (2 * n + dv)) & 7)) return QV_ERR_UNSUPPORTED;
   const bool grouped = max_q_len == 1 && H / G <= 16;
-  if (splits > 1 && (!grouped || !partial)) return QV_ERR_UNSUPPORTED;
+  if (splits > 1 && (!grouped || !partial || splits > 32)) return QV_ERR_UNSUPPORTED;
   if (S > 65535 || H > 65535) return QV_ERR_TOO_LARGE;
   cudaStream_t st = (cudaStream_t)stream;
   const int NT = diff_pad_n(n), DVT = diff_pad_dv(dv);
