@@ -202,15 +202,15 @@ def experts_case(T, peaks) -> dict:
 # Sixteen heads of two 64-wide maps over 128 values, four key/value heads, a window of 1,024 keys, rotation over the
 # whole map with stretching; dense feed-forwards of 8,192 alternate with 64 small experts of 1,024 of which 4 serve a
 # token beside a shared one of 2,048; the two middle layers run twice.
-LOT_ATTN = {"heads": 16, "kv_heads": 4, "dim": 64, "vdim": 128, "scale": 0.125, "diff": 0.3, "mask": {"size": 1024},
-            "rot": {"base": 250000.0, "dims": 64, "scaling": {"factor": 4.0, "original": 2048, "fast": 32.0, "slow": 1.0}}}
+LOT_ATTN = {"heads": 16, "kv_heads": 4, "dim": 64, "vdim": 128, "scale": 0.125, "diff": 0.2, "mask": {"size": 1024},
+            "rot": {"base": 500000.0, "dims": 64, "scaling": {"factor": 8.0, "original": 4096, "fast": 16.0, "slow": 2.0}}}
 LOT_DENSE = {"kind": "dense", "ff": 8192}
 LOT_MOE = {"kind": "moe", "expert": {"ff": 1024}, "router": {"experts": 64, "top": 4}, "shared": {"ff": 2048}}
 
 
 def lotirax_config() -> dict:
     layers = [{"type": "attention", "mixer": LOT_ATTN, "mlp": f} for f in (LOT_DENSE, LOT_MOE, LOT_DENSE, LOT_MOE)]
-    return {"architecture": "Lotirax", "vocab": VOCAB, "width": WIDTH, "norm": {"eps": 1e-5}, "residual_mult": 0.3, "layers": layers,
+    return {"architecture": "Lotirax", "vocab": VOCAB, "width": WIDTH, "norm": {"eps": 1e-5}, "residual_mult": 0.25, "layers": layers,
             "loop": {"start": 1, "stop": 3, "times": 2}}
 
 

@@ -63,7 +63,7 @@ CONFIG_B = config([layer(attn(heads=1, kv_heads=1, dim=36, vdim=24, window=17, r
 # C: the whole model runs three times from its first layer on; sizes in multiples of 16 and 32
 CONFIG_C = config([layer(attn(heads=4, kv_heads=2, dim=32, vdim=64, window=33, rot_dims=32), moe(experts=6, top=2, ff=32, shared=16)),
                    layer(attn(heads=4, kv_heads=4, dim=16, vdim=32, window=48, rot_dims=16), dense(ff=96))],
-                  vocab=190, width=64, eps=1e-5, mult=0.3, loop=(0, 2, 3))
+                  vocab=190, width=64, eps=4e-6, mult=0.35, loop=(0, 2, 3))
 # D: sizes that are multiples of neither 8 nor 16 anywhere (width, maps, values, feed-forwards, vocabulary), three query
 # heads on one key/value head, a stretch of one layer that runs once
 CONFIG_D = config([layer(attn(heads=3, kv_heads=1, dim=10, vdim=14, window=11, rot_dims=6), dense(ff=30)),

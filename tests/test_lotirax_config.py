@@ -70,7 +70,7 @@ def test_errors_name_the_key(change, key):
 
 
 @pytest.mark.parametrize("rot", [{"base": 3000.0, "dims": 16, "scaling": {"factor": 3.0, "original": 48, "fast": 6.0, "slow": 1.5}},
-                                 {"base": 250000.0, "dims": 64, "scaling": {"factor": 4.0, "original": 4096, "fast": 32.0, "slow": 1.0}},
+                                 {"base": 800000.0, "dims": 64, "scaling": {"factor": 6.0, "original": 4096, "fast": 24.0, "slow": 2.0}},
                                  {"base": 100.0, "dims": 8, "scaling": {"factor": 16.0, "original": 8, "fast": 1.0, "slow": 0.9}},
                                  {"base": 10000.0, "dims": 12}])
 def test_stretched_frequencies_against_the_plain_rule(rot):

@@ -86,7 +86,7 @@ MIXER_CASES = [lh.attn(), lh.attn(heads=3, kv_heads=3, dim=20, vdim=12, window=9
                lh.attn(heads=1, kv_heads=1, dim=36, vdim=24, window=17, rot_dims=0),
                lh.attn(heads=5, kv_heads=5, dim=12, vdim=28, window=64, rot_dims=12, scaling={"factor": 8.0, "original": 16, "fast": 4.0, "slow": 0.5}),
                lh.attn(heads=4, kv_heads=2, dim=32, vdim=64, window=33, rot_dims=32), lh.attn(heads=8, kv_heads=2, dim=64, vdim=128, window=0, rot_dims=32),
-               lh.attn(heads=4, kv_heads=4, dim=16, vdim=32, window=48, rot_dims=16), lh.attn(heads=2, kv_heads=2, dim=48, vdim=96, window=20, rot_dims=48),
+               lh.attn(heads=4, kv_heads=4, dim=16, vdim=32, window=48, rot_dims=16), lh.attn(heads=2, kv_heads=2, dim=40, vdim=88, window=20, rot_dims=40),
                lh.attn(heads=3, kv_heads=1, dim=7, vdim=70, window=5, rot_dims=6),
                lh.attn(heads=34, kv_heads=2, dim=8, vdim=8, window=30, rot_dims=8)]      # 17 query heads a key/value head: no shared tile
 
