@@ -219,7 +219,8 @@ extern "C" int qv_diff_attention_generic(void* out, int ld_out, const void* q, i
 // qv_diff_attention_tc       a CTA serves a tile of 16 * MW query rows of one segment and one head with 2 * MW warps: warps
 //                            0..MW-1 run map 1 and warps MW..2MW-1 map 2, each over 16 rows; blocks of 32 keys (both maps' key
 //                            entries and the values) come through a cp.async ring of four stages that both maps read; Q.K^T and P.V as
-//                            mma.sync m16n8k16 with float32 sums, softmax in float32 (base 2); at the end map 2's warps leave
+//                            mma.sync m16n8k16 with float32 sums, softmax in float32 (base 2), every weight entering P.V as three
+//                            bfloat16 terms that together hold its 24 bits; at the end map 2's warps leave
 //                            their normalised rows in shared memory and map 1's warps form a1 - lam * a2, the root mean square
 //                            over the head's values and the output.  Map and value sizes are padded with zeros up to the
 //                            template's (NT, DVT), so one instantiation serves all sizes below it (multiples of 8).
@@ -249,7 +250,7 @@ __device__ __forceinline__ uint32_t dpack(float lo, float hi) {
   return *(uint32_t*)&h;
 }
 
-template <int NT, int DVT, int MW, bool GROUPED, int STAGES>
+template <int NT, int DVT, int MW, bool GROUPED, int STAGES, int DIFF_P_TERMS>
 __global__ void __launch_bounds__(MW == 1 ? 128 : 64 * MW, MW == 1 ? 1 : (DVT <= 128 ? 2 : 1)) diff_attention_tc_kernel(
     bf16* __restrict__ out, int ld_out, const bf16* __restrict__ q, int ld_q, const bf16* __restrict__ cache,
     const int* __restrict__ seg_q_start, const int* __restrict__ seg_pos0, const int* __restrict__ block_table, int max_blocks,
@@ -449,16 +450,33 @@ __global__ void __launch_bounds__(MW == 1 ? 128 : 64 * MW, MW == 1 ? 1 : (DVT <=
 #pragma unroll
         for (int i = 0; i < DVT / 8; ++i) { o[i][0] *= corr[0]; o[i][1] *= corr[0]; o[i][2] *= corr[1]; o[i][3] *= corr[1]; }
       }
+      // The weights stay 32-bit in the product with the values: each is the sum of DIFF_P_TERMS bfloat16 terms (the value
+      // rounded, then what is left, rounded again, ...; three terms hold all 24 bits), and every term is multiplied.
 #pragma unroll
       for (int kc = 0; kc < DIFF_KB / 16; ++kc) {
-        uint32_t a[4] = {dpack(s[2 * kc][0], s[2 * kc][1]), dpack(s[2 * kc][2], s[2 * kc][3]),
-                         dpack(s[2 * kc + 1][0], s[2 * kc + 1][1]), dpack(s[2 * kc + 1][2], s[2 * kc + 1][3])};
+        float w[8] = {s[2 * kc][0], s[2 * kc][1], s[2 * kc][2], s[2 * kc][3], s[2 * kc + 1][0], s[2 * kc + 1][1], s[2 * kc + 1][2], s[2 * kc + 1][3]};
+        uint32_t a[DIFF_P_TERMS][4];
+#pragma unroll
+        for (int term = 0; term < DIFF_P_TERMS; ++term) {
+#pragma unroll
+          for (int x = 0; x < 4; ++x) {
+            const __nv_bfloat162 pr = __floats2bfloat162_rn(w[2 * x], w[2 * x + 1]);
+            a[term][x] = *(const uint32_t*)&pr;
+            if (term + 1 < DIFF_P_TERMS) {
+              w[2 * x] -= __low2float(pr);
+              w[2 * x + 1] -= __high2float(pr);
+            }
+          }
+        }
 #pragma unroll
         for (int nt = 0; nt < DVT / 16; ++nt) {
           uint32_t bfr[4];
           dldsm4t(bfr, Vs + (kc * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * LDV + nt * 16 + (lane >> 4) * 8);
-          dmma(o[2 * nt], a, bfr[0], bfr[1]);
-          dmma(o[2 * nt + 1], a, bfr[2], bfr[3]);
+#pragma unroll
+          for (int term = DIFF_P_TERMS - 1; term >= 0; --term) {      // the small terms first
+            dmma(o[2 * nt], a[term], bfr[0], bfr[1]);
+            dmma(o[2 * nt + 1], a[term], bfr[2], bfr[3]);
+          }
         }
       }
     }
@@ -590,6 +608,18 @@ __global__ void __launch_bounds__(128) diff_merge_kernel(bf16* __restrict__ out,
   }
 }
 
+// Into how many bfloat16 terms a softmax weight is split for the product with the values: 3 (all 24 bits: the weights are
+// 32-bit in that product), or 1 with QORVIX_DIFF_WEIGHT_TERMS=1 (rounded to bfloat16 as in the other attention kernels;
+// for comparison).
+static inline int diff_weight_terms() {
+  static int v = 0;
+  if (!v) {
+    const char* e = getenv("QORVIX_DIFF_WEIGHT_TERMS");
+    v = (e && e[0] == '1') ? 1 : 3;
+  }
+  return v;
+}
+
 static inline int diff_pad_n(int n) { return n <= 32 ? 32 : (n <= 64 ? 64 : 128); }
 static inline int diff_pad_dv(int dv) { return dv <= 64 ? 64 : (dv <= 128 ? 128 : 256); }
 
@@ -629,14 +659,14 @@ extern "C" int qv_diff_attention_tc(void* out, int ld_out, const void* q, int ld
   if (!grouped && tiles > 65535) return QV_ERR_TOO_LARGE;
   const dim3 grid(grouped ? splits : H, S, grouped ? G : tiles);
   int rc = QV_ERR_UNSUPPORTED;
-#define DIFF_LAUNCH_ST(N_, DV_, MW_, GR_, ST_)                                                                                      \
+#define DIFF_LAUNCH_PT(N_, DV_, MW_, GR_, PT_)                                                                                      \
   do {                                                                                                                              \
-    cudaFuncSetAttribute(diff_attention_tc_kernel<N_, DV_, MW_, GR_, ST_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
-    rc = qv_launch(diff_attention_tc_kernel<N_, DV_, MW_, GR_, ST_>, grid, dim3(MW_ == 1 ? 128 : 64 * MW_), smem, st, (bf16*)out,   \
+    cudaFuncSetAttribute(diff_attention_tc_kernel<N_, DV_, MW_, GR_, stages, PT_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+    rc = qv_launch(diff_attention_tc_kernel<N_, DV_, MW_, GR_, stages, PT_>, grid, dim3(MW_ == 1 ? 128 : 64 * MW_), smem, st, (bf16*)out, \
                    ld_out, (const bf16*)q, ld_q, (const bf16*)cache, seg_q_start, seg_pos0, block_table, max_blocks, H, G, n, dv,   \
                    page, page_shift, window, scale_log2, lam, eps, post, partial, splits);                                          \
   } while (0)
-#define DIFF_LAUNCH(N_, DV_, MW_, GR_) DIFF_LAUNCH_ST(N_, DV_, MW_, GR_, stages)
+#define DIFF_LAUNCH(N_, DV_, MW_, GR_) do { if (diff_weight_terms() == 1) DIFF_LAUNCH_PT(N_, DV_, MW_, GR_, 1); else DIFF_LAUNCH_PT(N_, DV_, MW_, GR_, 3); } while (0)
 #define DIFF_BY_MW(N_, DV_)                                                   \
   do {                                                                        \
     if (grouped) DIFF_LAUNCH(N_, DV_, 1, true);                               \
@@ -648,7 +678,7 @@ extern "C" int qv_diff_attention_tc(void* out, int ld_out, const void* q, int ld
 #undef DIFF_BY_DV
 #undef DIFF_BY_MW
 #undef DIFF_LAUNCH
-#undef DIFF_LAUNCH_ST
+#undef DIFF_LAUNCH_PT
   if (rc || splits <= 1) return rc;
   const int T = S;                                        // single tokens: a segment is a token
   const dim3 mgrid((T * H + 3) / 4);
