@@ -1,8 +1,6 @@
 """The Lotirax parts and the whole decoder against the plain implementation (tests/plain_lotirax.py): each mechanism
 alone in portions and token by token, windows' edges, one far key among hundreds, then whole models under every way of
 cutting, batching and reusing pages and slots, in float32 and bfloat16, and greedy generation through the scheduler."""
-import dataclasses
-
 import pytest
 import torch
 
