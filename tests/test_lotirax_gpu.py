@@ -86,7 +86,10 @@ MIXER_CASES = [lh.attn(), lh.attn(heads=3, kv_heads=3, dim=20, vdim=12, window=9
                lh.attn(heads=4, kv_heads=2, dim=32, vdim=64, window=33, rot_dims=32), lh.attn(heads=8, kv_heads=2, dim=64, vdim=128, window=0, rot_dims=32),
                lh.attn(heads=4, kv_heads=4, dim=16, vdim=32, window=48, rot_dims=16), lh.attn(heads=2, kv_heads=2, dim=40, vdim=88, window=20, rot_dims=40),
                lh.attn(heads=3, kv_heads=1, dim=7, vdim=70, window=5, rot_dims=6),
-               lh.attn(heads=34, kv_heads=2, dim=8, vdim=8, window=30, rot_dims=8)]      # 17 query heads a key/value head: no shared tile
+               lh.attn(heads=34, kv_heads=2, dim=8, vdim=8, window=30, rot_dims=8),      # 17 query heads a key/value head: no shared tile
+               lh.attn(heads=4, kv_heads=2, dim=72, vdim=136, window=50, rot_dims=36),   # the widest tiles: maps of up to 128, values of up to 256
+               lh.attn(heads=2, kv_heads=1, dim=128, vdim=256, window=0, rot_dims=128, scaling=None),
+               lh.attn(heads=2, kv_heads=2, dim=96, vdim=64, window=19, rot_dims=64), lh.attn(heads=3, kv_heads=3, dim=24, vdim=200, window=35, rot_dims=24)]
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
